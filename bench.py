@@ -1,0 +1,503 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-dequant hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-sweep]
+
+Headline workload (BASELINE config 2): W4A16 asymmetric GEMM, gs = 128,
+(N, K) = (14336, 4096), M = 1, x ~ N(0,1) FP16, W ~ N(0, 0.02) -- the shape the
+>= 75 %-of-HBM target is quoted on. A step is one GEMM call through the C ABI.
+The metric is the effective HBM rate, algorithmic bytes / time, in GB/s (its
+ratio to the peak is the "% of HBM roofline", its inverse the microseconds).
+
+  value      device-resident inputs, K steps captured in one CUDA graph
+             (weights rotate over enough copies to exceed the 126 MB L2)
+  e2e        the same GEMM through w4b_gemm_w4_hostio with HOST x and c
+  roofline   achieved GB/s of the GEMM kernel against the measured HBM peak
+  cpu_baseline / --impl reference
+             the reference's own CPU path (dequant_all + FP64 gemm_oracle; the
+             host quantizer is timed beside it) on all host cores
+
+Multi-GPU (torchrun, one rank per GPU): column-parallel along N with per-GPU work
+fixed (weak scaling): rank r owns rows [r*14336, (r+1)*14336) of a
+(14336*world) x 4096 matrix, x is replicated, and every step ends with an NCCL
+all-gather of the FP16 output slices.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_ROWS, K_COLS, GS, M_ROWS = 14336, 4096, 128, 1
+WORKLOAD = f"C2: W4A16 asym gs={GS} N={N_ROWS} K={K_COLS} M={M_ROWS}"
+
+
+def alg_bytes(N, K, gs, M, asym=True):
+    """Compulsory traffic of one GEMM (the reference's model, benchmarks/bench_fused.cu:384-387)."""
+    wk, G = (K + 7) // 8, (K + gs - 1) // gs
+    return N * wk * 4 + N * G * 2 + (N * ((G + 7) // 8) * 4 if asym else 0) + M * K * 2 + M * N * 2
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json, device copy)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+# ---------------------------------------------------------------------------
+# clocks sampler (nvidia-smi, read-only)
+# ---------------------------------------------------------------------------
+class Clocks:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+        except OSError:
+            self.proc = None
+            return
+        threading.Thread(target=self._read, daemon=True).start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        inside = [r for t, r in self.rows if t0 <= t <= t1]
+        window = "timed region"
+        if not inside:  # region shorter than the sampling period: fall back to the loaded part of the run
+            inside, window = [r for _, r in self.rows], "whole run (timed region shorter than one sample)"
+        sm, mx, reasons = [], [], set()
+        for r in inside:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
+
+
+# ---------------------------------------------------------------------------
+# synthetic weights (torch on the device; data generation only, never timed)
+# ---------------------------------------------------------------------------
+def make_w4_asym(torch, N, K, gs, seed, device):
+    """W ~ N(0, 0.02) quantised the way the format prescribes (groups widened to bracket 0,
+    scale stored in FP16, codes rounded against the stored scale)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    w = torch.randn(N, K, generator=g, device=device, dtype=torch.float32) * 0.02
+    G = K // gs
+    wg = w.view(N, G, gs)
+    lo = wg.amin(-1).clamp(max=0.0)
+    hi = wg.amax(-1).clamp(min=0.0)
+    s = torch.where(hi > lo, (hi - lo) / 15.0, torch.ones_like(hi)).to(torch.float16)
+    sf = s.float()
+    z = torch.round(-lo / sf).clamp(0, 15)
+    q = (torch.round(wg / sf[..., None]) + z[..., None]).clamp(0, 15).to(torch.int64).view(N, K // 8, 8)
+    sh = (4 * torch.arange(8, device=device, dtype=torch.int64))
+    qp = (q << sh).sum(-1)
+    qp = torch.where(qp >= 2**31, qp - 2**32, qp).to(torch.int32).contiguous()
+    wG = (G + 7) // 8
+    zp = torch.zeros(N, wG * 8, device=device, dtype=torch.int64)
+    zp[:, :G] = z.to(torch.int64)
+    zp = (zp.view(N, wG, 8) << sh).sum(-1)
+    zp = torch.where(zp >= 2**31, zp - 2**32, zp).to(torch.int32).contiguous()
+    wdeq = ((q.view(N, G, gs).float() - z[..., None]) * sf[..., None]).to(torch.float16).view(N, K)
+    return qp, s.contiguous(), zp, wdeq
+
+
+def run_mine(args):
+    import torch
+    import torch.distributed as dist
+
+    import w4a16_dequant_gemm_b200 as w4
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    N, K, gs, M = N_ROWS, K_COLS, GS, M_ROWS
+    bytes_per_gemm = alg_bytes(N, K, gs, M)
+    copies = max(2, -(-300_000_000 // bytes_per_gemm))  # rotate over > 2x the 126 MB L2
+    packs, wdeq0 = [], None
+    for i in range(copies):
+        qp, s, zp, wdeq = make_w4_asym(torch, N, K, gs, 1000 * rank + i, device)
+        if i == 0:
+            wdeq0 = wdeq
+        packs.append((qp, s, zp, w4.DevicePackedW(N, K, gs, K // gs, 0, qp.data_ptr(), s.data_ptr(), zp.data_ptr())))
+        del wdeq
+    g = torch.Generator(device=device).manual_seed(7)
+    x = torch.randn(M, K, generator=g, device=device, dtype=torch.float32).to(torch.float16)
+    c = torch.empty(M, N, device=device, dtype=torch.float16)
+    gathered = torch.empty(world, M, N, device=device, dtype=torch.float16) if world > 1 else None
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step(i):
+        w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, stream)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), c.view(-1))
+
+    # parity at bench size against a plain FP32 product of the dequantised weights
+    step(0)
+    torch.cuda.synchronize()
+    ref = x.float() @ wdeq0.float().t()
+    rel = float(((c.float() - ref).norm() / ref.norm()).item())
+    status = w4.device_status()
+    del wdeq0, ref
+    if status != 0 or not rel <= 1e-3:
+        raise SystemExit(f"bench: parity check failed (rel L2 {rel:.3e}, device status {status})")
+
+    clocks = Clocks(local)
+    if rank == 0:
+        clocks.start()
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    t_settle = time.time()
+    while time.time() - t_settle < 0.5:  # keep the GPU loaded until the clocks have settled
+        for i in range(200):
+            step(i)
+        torch.cuda.synchronize()
+
+    launches_before = w4.launch_count()
+    use_graph = world == 1
+    if use_graph:
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            sstream = side.cuda_stream
+            graph.capture_begin()
+            for i in range(args.steps):
+                w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, sstream)
+            graph.capture_end()
+        launches_captured = w4.launch_count() - launches_before
+        graph.replay()  # untimed: uploads the graph
+        torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    ev0.record()
+    if use_graph:
+        graph.replay()
+    else:
+        for i in range(args.steps):
+            step(i)
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t1 = time.time()
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    gpu_launches = launches_captured if use_graph else w4.launch_count() - launches_before
+    us_per_step = 1e3 * ms / args.steps
+    value = world * bytes_per_gemm / (us_per_step * 1e-6) / 1e9
+
+    # kernel-only duration for the roofline: the graph replays kernels back to back, so the
+    # per-launch duration is the step time at N = 1; under NCCL it is measured separately.
+    if use_graph:
+        kern_us = us_per_step
+    else:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(200):
+            w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, stream)
+        e1.record()
+        torch.cuda.synchronize()
+        kern_us = 1e3 * e0.elapsed_time(e1) / 200
+    peak, peak_src = measured_peak()
+    achieved = bytes_per_gemm / (kern_us * 1e-6) / 1e9
+
+    # end to end through the host-buffer entry: pinned x in, c out, every step
+    xh = x.cpu().pin_memory()
+    ch = torch.empty(M, N, dtype=torch.float16).pin_memory()
+    e2e_steps = min(args.steps, 2000)
+    for i in range(5):
+        w4.gemm_hostio(packs[i % copies][3], xh.data_ptr(), ch.data_ptr(), M, stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    te0 = time.perf_counter()
+    for i in range(e2e_steps):
+        w4.gemm_hostio(packs[i % copies][3], xh.data_ptr(), ch.data_ptr(), M, stream)
+    te = time.perf_counter() - te0
+    if world > 1:
+        t = torch.tensor([te], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        te = float(t.item())
+    e2e_value = world * bytes_per_gemm * e2e_steps / te / 1e9
+    clk = clocks.stop(t0, t1) if rank == 0 else None
+
+    extra = {}
+    if rank == 0 and world == 1 and not args.no_sweep:
+        extra = sweep(torch, w4, device, packs, copies)
+
+    cpu = cpu_baseline(quick=True) if (rank == 0 and world == 1) else None
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {
+        "metric": "w4a16_gemm_effective_hbm_rate", "value": round(value, 1), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": us_per_step / 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "us_per_gemm": round(us_per_step, 3),
+                   "algorithmic_bytes_per_gemm": bytes_per_gemm,
+                   "l2": f"weights rotate over {copies} copies ({copies * bytes_per_gemm / 1e6:.0f} MB > 126 MB L2)",
+                   "timing": "one CUDA graph of K launches, CUDA events" if use_graph else
+                             "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks",
+                   "parallelism": "single GPU" if world == 1 else f"column-parallel N x{world} + all-gather",
+                   "rel_l2_vs_fp32_product": rel},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                     "peak_source": peak_src, "frac_of_nominal_8TBs": round(achieved / 8000.0, 4),
+                     "kernel_us": round(kern_us, 3)},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": M * K * 2,
+                "d2h_bytes_per_step": M * N * 2, "us_per_step": round(1e6 * te / e2e_steps, 2), "steps": e2e_steps},
+        "gpu_launches": int(gpu_launches),
+        "clocks": clk,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    if extra:
+        line["extra"] = extra
+    print(json.dumps(line))
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one stream-GEMM launch at the headline
+# shape, from the ncu capture summarised under profiles/ (None until one has been taken).
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def time_graph(torch, fn, n):
+    """Average microseconds of fn(i) over n calls captured in one CUDA graph."""
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        graph.capture_begin()
+        for i in range(n):
+            fn(i, side.cuda_stream)
+        graph.capture_end()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return 1e3 * e0.elapsed_time(e1) / n
+
+
+def sweep(torch, w4, device, packs, copies):
+    """Secondary numbers of the metric: GEMM microseconds at M = 1..256 for both C2 orientations and
+    flash-decode microseconds per step (config 4, B*H = 256, S = 8192, D = 128) for FP16 / W4 / FP8."""
+    out = {"gemm_us": {}, "flash_decode_us": {}}
+    peak, _ = measured_peak()
+    N, K, gs = N_ROWS, K_COLS, GS
+    for M in (1, 4, 8, 9, 16, 64, 256):
+        x = torch.randn(M, K, device=device).to(torch.float16)
+        c = torch.empty(M, N, device=device, dtype=torch.float16)
+        for i in range(3):
+            w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M)
+        us = time_graph(torch, lambda i, s: w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, s), 4 * copies)
+        b = alg_bytes(N, K, gs, M)
+        out["gemm_us"][f"N{N}_K{K}_M{M}"] = {"us": round(us, 2), "GBps": round(b / us / 1e3, 1),
+                                              "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3),
+                                              "TFLOPs": round(2.0 * M * N * K / us / 1e6, 2)}
+    # the transposed orientation (N, K) = (4096, 14336)
+    N2, K2 = K_COLS, N_ROWS
+    packs2 = []
+    for i in range(copies):
+        qp, s, zp, _ = make_w4_asym(torch, N2, K2, gs, 500 + i, device)
+        packs2.append((qp, s, zp, w4.DevicePackedW(N2, K2, gs, K2 // gs, 0, qp.data_ptr(), s.data_ptr(), zp.data_ptr())))
+    for M in (1, 4, 16):
+        x = torch.randn(M, K2, device=device).to(torch.float16)
+        c = torch.empty(M, N2, device=device, dtype=torch.float16)
+        for i in range(3):
+            w4.gemm(packs2[i % copies][3], x.data_ptr(), c.data_ptr(), M)
+        us = time_graph(torch, lambda i, s: w4.gemm(packs2[i % copies][3], x.data_ptr(), c.data_ptr(), M, s), 4 * copies)
+        b = alg_bytes(N2, K2, gs, M)
+        out["gemm_us"][f"N{N2}_K{K2}_M{M}"] = {"us": round(us, 2), "GBps": round(b / us / 1e3, 1),
+                                                "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3)}
+    del packs2
+    # flash decode: random cache bytes are as good as quantised ones for timing
+    H, S, D, g = 256, 8192, 128, 32
+    q = torch.randn(H, D, device=device).to(torch.float16)
+    o = torch.empty(H, D, device=device, dtype=torch.float16)
+    k16 = torch.randn(H, S, D, device=device).to(torch.float16)
+    v16 = torch.randn(H, S, D, device=device).to(torch.float16)
+    for i in range(2):
+        w4.attention_fp16_flash(q.data_ptr(), k16.data_ptr(), v16.data_ptr(), o.data_ptr(), H, S, D)
+    us = time_graph(torch, lambda i, s: w4.attention_fp16_flash(q.data_ptr(), k16.data_ptr(), v16.data_ptr(),
+                                                               o.data_ptr(), H, S, D, s), 5)
+    b = 2 * H * S * D * 2
+    out["flash_decode_us"]["fp16"] = {"us": round(us, 1), "GBps": round(b / us / 1e3, 1),
+                                      "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3)}
+    del k16, v16
+    G = D // g
+    qk = torch.randint(-2**31, 2**31 - 1, (H, S, D // 8), device=device, dtype=torch.int32)
+    qv = torch.randint(-2**31, 2**31 - 1, (H, S, D // 8), device=device, dtype=torch.int32)
+    sk = (torch.rand(H, S, G, device=device) * 0.1 + 0.05).to(torch.float16)
+    sv = (torch.rand(H, S, G, device=device) * 0.1 + 0.05).to(torch.float16)
+    kv = w4.DeviceKVW4(H, S, D, g, G, 1, qk.data_ptr(), sk.data_ptr(), None, qv.data_ptr(), sv.data_ptr(), None)
+    for i in range(2):
+        w4.attention_w4_flash(kv, q.data_ptr(), o.data_ptr())
+    us = time_graph(torch, lambda i, s: w4.attention_w4_flash(kv, q.data_ptr(), o.data_ptr(), s), 5)
+    b = 2 * H * S * (D // 2 + G * 2)
+    out["flash_decode_us"]["w4_gs32"] = {"us": round(us, 1), "GBps": round(b / us / 1e3, 1),
+                                         "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3)}
+    del qk, qv
+    bk = torch.randint(0, 0x7E, (H, S, D), device=device, dtype=torch.uint8)
+    bv = torch.randint(0, 0x7E, (H, S, D), device=device, dtype=torch.uint8)
+    f8 = w4.DeviceKVF8(H, S, D, g, G, bk.data_ptr(), sk.data_ptr(), bv.data_ptr(), sv.data_ptr())
+    for i in range(2):
+        w4.attention_f8_flash(f8, q.data_ptr(), o.data_ptr())
+    us = time_graph(torch, lambda i, s: w4.attention_f8_flash(f8, q.data_ptr(), o.data_ptr(), s), 5)
+    b = 2 * H * S * (D + G * 2)
+    out["flash_decode_us"]["f8_gs32"] = {"us": round(us, 1), "GBps": round(b / us / 1e3, 1),
+                                         "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3)}
+    out["flash_decode_us"]["shape"] = f"B*H={H} S={S} D={D} gs={g}"
+    assert w4.device_status() == 0
+    return out
+
+
+# ---------------------------------------------------------------------------
+# the reference's CPU path, timed on the host cores
+# ---------------------------------------------------------------------------
+def cpu_engine():
+    from oracle import orc
+    if orc.have_reference():
+        return orc.Reference(), "reference"
+    return orc.Oracle(), "port"
+
+
+def cpu_step(eng, kind, orc_lib, rows, threads, packed, x16):
+    """One pass of the reference CPU path over a `rows`-row slice of the headline workload:
+    dequant_all then the FP64 gemm_oracle. Returns seconds."""
+    t0 = time.perf_counter()
+    if kind == "reference":
+        eng.cpu_path_w4(None, x16, M_ROWS, rows, K_COLS, GS, False, threads, packed=packed)
+    else:
+        wd = eng.dequant_all_w4(packed)
+        eng.gemm_oracle(x16, M_ROWS, K_COLS, wd, rows, threads=threads)
+    return time.perf_counter() - t0
+
+
+def cpu_sample(rows):
+    import numpy as np
+    from oracle import orc
+    o = orc.Oracle()
+    w = o.normal_f64(rows * K_COLS, 0) * 0.02
+    t0 = time.perf_counter()
+    packed = o.quantize_w4(w, rows, K_COLS, GS, False)
+    tq = time.perf_counter() - t0
+    x16 = o.normal_f16(M_ROWS * K_COLS, 1)
+    return packed, x16, tq
+
+
+def cpu_baseline(quick):
+    threads = os.cpu_count() or 1
+    eng, kind = cpu_engine()
+    rows = 2048 if quick else 2048
+    packed, x16, tq = cpu_sample(rows)
+    cpu_step(eng, kind, None, rows, threads, packed, x16)  # warm
+    reps, t = 0, 0.0
+    while t < (3.0 if quick else 10.0) and reps < 200:
+        t += cpu_step(eng, kind, None, rows, threads, packed, x16)
+        reps += 1
+    per = t / reps
+    b = alg_bytes(rows, K_COLS, GS, M_ROWS)
+    return {"value": round(b / per / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": f"{rows} of {N_ROWS} rows of the headline GEMM (K={K_COLS}, gs={GS}, M={M_ROWS}); "
+                      f"dequant_all + FP64 gemm_oracle, row-sliced over {threads} threads, {reps} reps; "
+                      f"single-threaded host quantize of the slice took {tq:.2f} s (not in the value)",
+            "us_per_full_gemm_extrapolated": round(per * N_ROWS / rows * 1e6, 1)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    eng, kind = cpu_engine()
+    # Size the per-step sample so that steps + warm-up end within about two minutes.
+    probe_rows = 256
+    packed, x16, _ = cpu_sample(probe_rows)
+    cpu_step(eng, kind, None, probe_rows, threads, packed, x16)
+    per_row = min(cpu_step(eng, kind, None, probe_rows, threads, packed, x16) for _ in range(3)) / probe_rows
+    warm = max(args.warmup, 1)
+    rows = int(120.0 / ((args.steps + warm) * per_row))
+    rows = max(64, min(N_ROWS, rows)) // 64 * 64
+    packed, x16, tq = cpu_sample(rows)
+    for _ in range(warm):
+        cpu_step(eng, kind, None, rows, threads, packed, x16)
+    t = 0.0
+    for _ in range(args.steps):
+        t += cpu_step(eng, kind, None, rows, threads, packed, x16)
+    per = t / args.steps
+    b = alg_bytes(rows, K_COLS, GS, M_ROWS)
+    value = round(b / per / 1e9, 4)
+    sample = (f"each step = the reference CPU path (dequant_all + FP64 gemm_oracle) over {rows} of {N_ROWS} rows "
+              f"of the headline GEMM, row-sliced over {threads} host threads")
+    print(json.dumps({
+        "impl": "reference", "metric": "w4a16_gemm_effective_hbm_rate", "value": value, "unit": "GB/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": warm,
+        "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64", "data": "synthetic", "config": {"workload": WORKLOAD, "sample_rows": rows},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="mine", choices=["mine", "reference"])
+    ap.add_argument("--no-sweep", action="store_true")
+    args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 20000 if args.impl == "mine" else 50
+    if args.warmup is None:
+        args.warmup = 20 if args.impl == "mine" else 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_mine(args)
+
+
+if __name__ == "__main__":
+    main()

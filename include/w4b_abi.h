@@ -1,0 +1,166 @@
+/*
+ * w4b_abi.h -- C ABI of the B200 (sm_100a) fused-dequant library, libw4b200.so.
+ *
+ * One entry point per host entry of the reference project's GPU API
+ * (namespace w4::gpu); each declaration cites the reference interface it
+ * replaces by file:line (paths relative to the reference project's root).
+ * Plain pointers and sizes only; all data pointers are DEVICE pointers unless
+ * a parameter is named *_host. `stream` is a cudaStream_t passed as void*
+ * (NULL = the default stream). Calls are asynchronous with respect to the host
+ * exactly like the reference's launchers: only launch-time errors are reported.
+ *
+ * Return value: W4B_OK, or
+ *   W4B_INVALID  a contract violation -- what the reference reports by throwing
+ *                std::invalid_argument. Detected on the host BEFORE any
+ *                allocation or launch; no pointer is dereferenced.
+ *   W4B_CUDA     a CUDA runtime failure -- the reference's std::runtime_error.
+ * w4b_last_error() returns the message of the calling thread's last failure.
+ *
+ * Like the reference (include/w4/fused.cuh:51-54, include/w4/kvflash.cuh:56-57)
+ * the library keeps grow-only device scratch per device; calls that use it must
+ * not be in flight concurrently on different streams of one device.
+ */
+#ifndef W4B_ABI_H_
+#define W4B_ABI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define W4B_OK 0
+#define W4B_INVALID 1
+#define W4B_CUDA 2
+
+/* Which GEMM kernel serves a call. AUTO applies the library's crossover
+ * (w4b_dispatch_mma_min_m); the others pin one kernel so that the reference's
+ * separately addressable entries gemm_fused / gemm_mma stay addressable. */
+#define W4B_PATH_AUTO 0
+#define W4B_PATH_STREAM 1  /* replaces gemm_fused / gemm_fused_mx: HBM-streaming kernel   */
+#define W4B_PATH_TENSOR 2  /* replaces gemm_mma / gemm_mma_mx: tcgen05 / TMEM kernel      */
+#define W4B_PATH_GENERIC 3 /* shape-agnostic kernel behind both (ragged K, odd gs, ...)    */
+
+/* Packed W4 weights. Field order and meaning of DevicePackedW
+ * (include/w4/dequant.cuh:31-37); format of include/w4/pack.hpp:3-14:
+ * q N*words(K) uint32, nibble j of word w is k = 8w+j, low nibble first;
+ * scales N*G FP16; zeros N*words(G) uint32 (asymmetric only, NULL otherwise). */
+typedef struct w4b_packed_w4 {
+  int N, K, gs, G;
+  int symmetric;
+  const uint32_t* q;
+  const uint16_t* scales; /* FP16 bit patterns */
+  const uint32_t* zeros;
+} w4b_packed_w4;
+
+/* Packed MXFP4 weights: DevicePackedWm (include/w4/mxfused.cuh:26-30);
+ * format of include/w4/mx.hpp:10-14: E2M1 codes packed like q above, one E8M0
+ * byte per (row, 32-element block), B = ceil(K/32). */
+typedef struct w4b_packed_mx {
+  int N, K, B;
+  const uint32_t* q;
+  const uint8_t* scales;
+} w4b_packed_mx;
+
+/* W4 KV cache: DeviceKVW4 (include/w4/kvattention.cuh:39-48). H head slabs of
+ * the W4 format with rows = positions and K axis = D. For the paged entry the
+ * slab of one head has npages*page rows and S is the logical length. */
+typedef struct w4b_kv_w4 {
+  int H, S, D, gs, G;
+  int symmetric;
+  const uint32_t* q_k;
+  const uint16_t* s_k;
+  const uint32_t* z_k;
+  const uint32_t* q_v;
+  const uint16_t* s_v;
+  const uint32_t* z_v;
+} w4b_kv_w4;
+
+/* FP8 E4M3 KV cache: DeviceKVF8 (include/w4/kvflash.cuh:390-396): one byte per
+ * element [H][S][D], one FP16 scale per (position, group). */
+typedef struct w4b_kv_f8 {
+  int H, S, D, gs, G;
+  const uint8_t* q_k;
+  const uint16_t* s_k;
+  const uint8_t* q_v;
+  const uint16_t* s_v;
+} w4b_kv_f8;
+
+/* ---- library state ---------------------------------------------------- */
+
+const char* w4b_last_error(void);
+/* M at or above this goes to the tensor kernel under W4B_PATH_AUTO; replaces
+ * the constant DISPATCH_MMA_MIN_M (include/w4/dispatch.cuh:25). */
+int w4b_dispatch_mma_min_m(void);
+/* Which kernel W4B_PATH_AUTO (or a pinned path) would run for this shape:
+ * returns a W4B_PATH_* value >= 1, or -1 when the arguments are invalid. */
+int w4b_gemm_w4_route(const w4b_packed_w4* p, int M, int path, const void* x);
+int w4b_gemm_mx_route(const w4b_packed_mx* p, int M, int path, const void* x);
+/* Synchronises the current device and returns the kernels' own status word:
+ * 0, or a non-zero code when a bounded device-side wait gave up (the kernel
+ * then returned early and its output is undefined). Clears the word. */
+int w4b_device_status(void);
+/* Number of kernel launches this library has issued from the calling process. */
+unsigned long long w4b_launch_count(void);
+
+/* ---- fused dequant GEMM: C[M,N] = X[M,K] * dequant(W)[N,K]^T ----------- */
+
+/* gemm / gemm_fused / gemm_mma (include/w4/dispatch.cuh:27-34,
+ * include/w4/fused.cuh:172-214, include/w4/mma.cuh:234-260).
+ * x: M*K FP16 row-major, c: M*N FP16 row-major. w_out (optional, N*K FP16)
+ * receives every dequantised weight, bit-identical to the host dequant_all. */
+int w4b_gemm_w4(const w4b_packed_w4* p, const void* x, void* c, int M, int path, void* stream,
+                void* w_out);
+/* gemm_mx / gemm_fused_mx / gemm_mma_mx (include/w4/dispatch.cuh:36-43,
+ * include/w4/mxfused.cuh:166-198,291-307). */
+int w4b_gemm_mx(const w4b_packed_mx* p, const void* x, void* c, int M, int path, void* stream,
+                void* w_out);
+
+/* The same GEMM through HOST activation / output buffers: copies x_host to the
+ * device, runs w4b_gemm_w4 (weights stay resident on the device), copies the
+ * result into c_host and waits for it. This is the call an application that
+ * keeps activations on the host makes; the reference has no such entry (its
+ * tests do the two cudaMemcpy themselves, tests/test_gpu.cu:109-113,177-181). */
+int w4b_gemm_w4_hostio(const w4b_packed_w4* p, const void* x_host, void* c_host, int M, int path,
+                       void* stream);
+
+/* ---- stand-alone dequantisation (two-pass comparator, bitwise gate) ---- */
+
+/* dequant (include/w4/dequant.cuh:62-82): w is N*K FP16. */
+int w4b_dequant_w4(const w4b_packed_w4* p, void* w, void* stream);
+/* dequant_mx (include/w4/mxfused.cuh:57-69). */
+int w4b_dequant_mx(const w4b_packed_mx* p, void* w, void* stream);
+/* dequant_f8 (include/w4/kvflash.cuh:435-457): one head, q S*D bytes, s S*G. */
+int w4b_dequant_f8(const uint8_t* q, const uint16_t* s, void* w, int S, int D, int gs, void* stream);
+
+/* ---- decode attention, one query token per head ----------------------- */
+
+/* attention_fp16_flash (include/w4/kvflash.cuh:365-384): q H*D, k16/v16
+ * [H][S][D] FP16, out H*D FP16. */
+int w4b_attn_flash_fp16(const void* q, const void* k16, const void* v16, void* out, int H, int S,
+                        int D, void* stream);
+/* attention_w4_flash (include/w4/kvflash.cuh:350-363). k_out / v_out (optional,
+ * H*S*D FP16 each) receive the dequantised cache, bit-identical to dequant_head. */
+int w4b_attn_flash_w4(const w4b_kv_w4* p, const void* q, void* out, void* stream, void* k_out,
+                      void* v_out);
+/* attention_f8_flash (include/w4/kvflash.cuh:572-590). */
+int w4b_attn_flash_f8(const w4b_kv_f8* p, const void* q, void* out, void* stream, void* k_out,
+                      void* v_out);
+/* attention_w4_flash_paged (include/w4/kvflash.cuh:725-764): logical position t
+ * of every head lives at pool row bt[t/page]*page + t%page; bt has
+ * ceil(S/page) int32 entries on the device; hooks write in logical order. */
+int w4b_attn_flash_w4_paged(const w4b_kv_w4* p, const int* bt, int page, int npages, const void* q,
+                            void* out, void* stream, void* k_out, void* v_out);
+/* attention_fp16 / attention_w4 (include/w4/kvattention.cuh:226-248): the
+ * legacy single-block entries; same results contract, and they keep the
+ * reference's S <= 4096 and D <= 512 rejections. */
+int w4b_attn_single_fp16(const void* q, const void* k16, const void* v16, void* out, int H, int S,
+                         int D, void* stream);
+int w4b_attn_single_w4(const w4b_kv_w4* p, const void* q, void* out, void* stream, void* k_out,
+                       void* v_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4B_ABI_H_ */

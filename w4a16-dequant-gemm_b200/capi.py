@@ -1,0 +1,248 @@
+"""ctypes binding of the C ABI (include/w4b_abi.h) and a host-side mirror of the
+reference's GPU entry points (namespace w4::gpu): same names, argument order
+and error behaviour, so that tests read like the reference's own.
+
+Contract violations raise ``InvalidArgument`` (the reference's
+std::invalid_argument), CUDA failures raise ``CudaError`` (its
+std::runtime_error). Device buffers are passed as integers (device addresses),
+e.g. ``tensor.data_ptr()``; nothing here allocates or touches device memory.
+There is no CPU fallback: without the compiled library the import fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+from . import build as _build
+
+PATH_AUTO, PATH_STREAM, PATH_TENSOR, PATH_GENERIC = 0, 1, 2, 3
+
+
+class InvalidArgument(ValueError):
+    """A contract violation, rejected on the host before any launch."""
+
+
+class CudaError(RuntimeError):
+    """A CUDA runtime failure reported by the library."""
+
+
+class _PackedW4(C.Structure):
+    _fields_ = [("N", C.c_int), ("K", C.c_int), ("gs", C.c_int), ("G", C.c_int), ("symmetric", C.c_int),
+                ("q", C.c_void_p), ("scales", C.c_void_p), ("zeros", C.c_void_p)]
+
+
+class _PackedMx(C.Structure):
+    _fields_ = [("N", C.c_int), ("K", C.c_int), ("B", C.c_int), ("q", C.c_void_p), ("scales", C.c_void_p)]
+
+
+class _KvW4(C.Structure):
+    _fields_ = [("H", C.c_int), ("S", C.c_int), ("D", C.c_int), ("gs", C.c_int), ("G", C.c_int),
+                ("symmetric", C.c_int), ("q_k", C.c_void_p), ("s_k", C.c_void_p), ("z_k", C.c_void_p),
+                ("q_v", C.c_void_p), ("s_v", C.c_void_p), ("z_v", C.c_void_p)]
+
+
+class _KvF8(C.Structure):
+    _fields_ = [("H", C.c_int), ("S", C.c_int), ("D", C.c_int), ("gs", C.c_int), ("G", C.c_int),
+                ("q_k", C.c_void_p), ("s_k", C.c_void_p), ("q_v", C.c_void_p), ("s_v", C.c_void_p)]
+
+
+# Every symbol include/w4b_abi.h declares: name -> (restype, argtypes)
+_P, _I = C.c_void_p, C.c_int
+ABI = {
+    "w4b_last_error": (C.c_char_p, []),
+    "w4b_dispatch_mma_min_m": (_I, []),
+    "w4b_gemm_w4_route": (_I, [C.POINTER(_PackedW4), _I, _I, _P]),
+    "w4b_gemm_mx_route": (_I, [C.POINTER(_PackedMx), _I, _I, _P]),
+    "w4b_device_status": (_I, []),
+    "w4b_launch_count": (C.c_ulonglong, []),
+    "w4b_gemm_w4": (_I, [C.POINTER(_PackedW4), _P, _P, _I, _I, _P, _P]),
+    "w4b_gemm_mx": (_I, [C.POINTER(_PackedMx), _P, _P, _I, _I, _P, _P]),
+    "w4b_gemm_w4_hostio": (_I, [C.POINTER(_PackedW4), _P, _P, _I, _I, _P]),
+    "w4b_dequant_w4": (_I, [C.POINTER(_PackedW4), _P, _P]),
+    "w4b_dequant_mx": (_I, [C.POINTER(_PackedMx), _P, _P]),
+    "w4b_dequant_f8": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "w4b_attn_flash_fp16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
+    "w4b_attn_flash_w4": (_I, [C.POINTER(_KvW4), _P, _P, _P, _P, _P]),
+    "w4b_attn_flash_f8": (_I, [C.POINTER(_KvF8), _P, _P, _P, _P, _P]),
+    "w4b_attn_flash_w4_paged": (_I, [C.POINTER(_KvW4), _P, _I, _I, _P, _P, _P, _P, _P]),
+    "w4b_attn_single_fp16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
+    "w4b_attn_single_w4": (_I, [C.POINTER(_KvW4), _P, _P, _P, _P, _P]),
+}
+
+
+def _load():
+    path = _build.LIB
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: build it with `python w4a16-dequant-gemm_b200/build.py` "
+                          "(there is no CPU fallback)")
+    dll = C.CDLL(path)
+    for name, (res, args) in ABI.items():
+        fn = getattr(dll, name)
+        fn.restype, fn.argtypes = res, args
+    return dll
+
+
+lib = _load()
+
+
+def _check(rc: int):
+    if rc == 0:
+        return
+    msg = lib.w4b_last_error().decode()
+    if rc == 1:
+        raise InvalidArgument(msg)
+    raise CudaError(msg)
+
+
+# ---- the reference's descriptor structs, as plain Python ------------------
+
+@dataclass
+class DevicePackedW:  # include/w4/dequant.cuh:31-37
+    N: int
+    K: int
+    gs: int
+    G: int
+    symmetric: int
+    q: int
+    scales: int
+    zeros: Optional[int] = None
+
+    def _c(self):
+        return _PackedW4(self.N, self.K, self.gs, self.G, int(self.symmetric), self.q, self.scales, self.zeros)
+
+
+@dataclass
+class DevicePackedWm:  # include/w4/mxfused.cuh:26-30
+    N: int
+    K: int
+    B: int
+    q: int
+    scales: int
+
+    def _c(self):
+        return _PackedMx(self.N, self.K, self.B, self.q, self.scales)
+
+
+@dataclass
+class DeviceKVW4:  # include/w4/kvattention.cuh:39-48
+    H: int
+    S: int
+    D: int
+    gs: int
+    G: int
+    symmetric: int
+    q_k: int
+    s_k: int
+    z_k: Optional[int]
+    q_v: int
+    s_v: int
+    z_v: Optional[int]
+
+    def _c(self):
+        return _KvW4(self.H, self.S, self.D, self.gs, self.G, int(self.symmetric), self.q_k, self.s_k, self.z_k,
+                     self.q_v, self.s_v, self.z_v)
+
+
+@dataclass
+class DeviceKVF8:  # include/w4/kvflash.cuh:390-396
+    H: int
+    S: int
+    D: int
+    gs: int
+    G: int
+    q_k: int
+    s_k: int
+    q_v: int
+    s_v: int
+
+    def _c(self):
+        return _KvF8(self.H, self.S, self.D, self.gs, self.G, self.q_k, self.s_k, self.q_v, self.s_v)
+
+
+# ---- entry points, named as in the reference ------------------------------
+
+def DISPATCH_MMA_MIN_M() -> int:  # include/w4/dispatch.cuh:25
+    return lib.w4b_dispatch_mma_min_m()
+
+
+def gemm(p: DevicePackedW, x, c, M, stream=None, w_out=None, path=PATH_AUTO):  # dispatch.cuh:27
+    _check(lib.w4b_gemm_w4(C.byref(p._c()), x, c, M, path, stream, w_out))
+
+
+def gemm_fused(p, x, c, M, stream=None, w_out=None):  # fused.cuh:172
+    gemm(p, x, c, M, stream, w_out, PATH_STREAM)
+
+
+def gemm_mma(p, x, c, M, stream=None, w_out=None):  # mma.cuh:234
+    gemm(p, x, c, M, stream, w_out, PATH_TENSOR)
+
+
+def gemm_mx(p: DevicePackedWm, x, c, M, stream=None, w_out=None, path=PATH_AUTO):  # dispatch.cuh:36
+    _check(lib.w4b_gemm_mx(C.byref(p._c()), x, c, M, path, stream, w_out))
+
+
+def gemm_fused_mx(p, x, c, M, stream=None, w_out=None):  # mxfused.cuh:166
+    gemm_mx(p, x, c, M, stream, w_out, PATH_STREAM)
+
+
+def gemm_mma_mx(p, x, c, M, stream=None, w_out=None):  # mxfused.cuh:291
+    gemm_mx(p, x, c, M, stream, w_out, PATH_TENSOR)
+
+
+def gemm_hostio(p: DevicePackedW, x_host, c_host, M, stream=None, path=PATH_AUTO):
+    """x_host / c_host are HOST addresses (pinned for full speed); weights stay on the device."""
+    _check(lib.w4b_gemm_w4_hostio(C.byref(p._c()), x_host, c_host, M, path, stream))
+
+
+def gemm_route(p, M, path=PATH_AUTO, x=16) -> int:
+    if isinstance(p, DevicePackedWm):
+        return lib.w4b_gemm_mx_route(C.byref(p._c()), M, path, x)
+    return lib.w4b_gemm_w4_route(C.byref(p._c()), M, path, x)
+
+
+def dequant(p: DevicePackedW, w, stream=None):  # dequant.cuh:62
+    _check(lib.w4b_dequant_w4(C.byref(p._c()), w, stream))
+
+
+def dequant_mx(p: DevicePackedWm, w, stream=None):  # mxfused.cuh:57
+    _check(lib.w4b_dequant_mx(C.byref(p._c()), w, stream))
+
+
+def dequant_f8(q, s, w, S, D, gs, stream=None):  # kvflash.cuh:435
+    _check(lib.w4b_dequant_f8(q, s, w, S, D, gs, stream))
+
+
+def attention_fp16_flash(q, k16, v16, out, H, S, D, stream=None):  # kvflash.cuh:365
+    _check(lib.w4b_attn_flash_fp16(q, k16, v16, out, H, S, D, stream))
+
+
+def attention_w4_flash(p: DeviceKVW4, q, out, stream=None, k_out=None, v_out=None):  # kvflash.cuh:350
+    _check(lib.w4b_attn_flash_w4(C.byref(p._c()), q, out, stream, k_out, v_out))
+
+
+def attention_f8_flash(p: DeviceKVF8, q, out, stream=None, k_out=None, v_out=None):  # kvflash.cuh:572
+    _check(lib.w4b_attn_flash_f8(C.byref(p._c()), q, out, stream, k_out, v_out))
+
+
+def attention_w4_flash_paged(p: DeviceKVW4, bt, page, npages, q, out, stream=None, k_out=None,
+                             v_out=None):  # kvflash.cuh:725
+    _check(lib.w4b_attn_flash_w4_paged(C.byref(p._c()), bt, page, npages, q, out, stream, k_out, v_out))
+
+
+def attention_fp16(q, k16, v16, out, H, S, D, stream=None):  # kvattention.cuh:226
+    _check(lib.w4b_attn_single_fp16(q, k16, v16, out, H, S, D, stream))
+
+
+def attention_w4(p: DeviceKVW4, q, out, stream=None, k_out=None, v_out=None):  # kvattention.cuh:241
+    _check(lib.w4b_attn_single_w4(C.byref(p._c()), q, out, stream, k_out, v_out))
+
+
+def device_status() -> int:
+    """Synchronises and returns (then clears) the kernels' status word; 0 is healthy."""
+    return lib.w4b_device_status()
+
+
+def launch_count() -> int:
+    return int(lib.w4b_launch_count())

@@ -1,0 +1,446 @@
+// The C ABI of libw4b200 (include/w4b_abi.h): argument validation with the
+// reference's reject-before-touching contract, per-device scratch, routing
+// between the kernels, and error reporting. No kernel lives in this file.
+#include "../../include/w4b_abi.h"
+
+#include <limits.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "w4b_kernels.h"
+
+namespace {
+
+using namespace w4b;
+
+thread_local char g_err[512] = "";
+std::atomic<unsigned long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(W4B_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define INVALID(...) return fail(W4B_INVALID, __VA_ARGS__)
+#define CUDA_TRY(expr, what)                         \
+  do {                                               \
+    const cudaError_t e_ = (expr);                   \
+    if (e_ != cudaSuccess) return cuda_fail(e_, what); \
+  } while (0)
+
+// The crossover between the stream kernel and the tensor kernel under
+// W4B_PATH_AUTO (the reference's DISPATCH_MMA_MIN_M, include/w4/dispatch.cuh:25).
+constexpr int kMmaMinM = 17;
+
+// Grow-only device buffer. Like the reference's function-static scratch
+// (include/w4/fused.cuh:55-66) it is shared by all calls on a device.
+struct Scratch {
+  void* ptr = nullptr;
+  size_t cap = 0;
+  // Grows to at least `bytes`; `zero` clears a newly allocated buffer.
+  cudaError_t reserve(size_t bytes, bool zero) {
+    if (bytes <= cap) return cudaSuccess;
+    void* nb = nullptr;
+    size_t want = bytes < 4096 ? 4096 : bytes;
+    cudaError_t e = cudaMalloc(&nb, want);
+    if (e != cudaSuccess) return e;
+    if (zero) {
+      e = cudaMemset(nb, 0, want);
+      if (e != cudaSuccess) {
+        cudaFree(nb);
+        return e;
+      }
+    }
+    if (ptr) cudaFree(ptr);  // implicit device synchronisation: no kernel still uses it
+    ptr = nb;
+    cap = want;
+    return cudaSuccess;
+  }
+};
+
+struct DeviceCtx {
+  bool ready = false;
+  int sm_count = 0;
+  int* status = nullptr;  // device status word written by bounded waits
+  Scratch gemm_ws;        // FP32 partial fragments of split panels
+  Scratch gemm_counters;  // arrival counters, zero between launches
+  Scratch attn_ws;        // (m, l, acc[D]) partials of split sequences
+  Scratch io_x, io_c;     // device staging of the host-buffer entry
+};
+
+constexpr int kMaxDevices = 64;
+DeviceCtx g_ctx[kMaxDevices];
+std::mutex g_mu;
+
+int get_ctx(DeviceCtx** out) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev), "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return fail(W4B_CUDA, "device index %d out of range", dev);
+  DeviceCtx& c = g_ctx[dev];
+  if (!c.ready) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!c.ready) {
+      CUDA_TRY(cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev), "device attribute");
+      int major = 0;
+      CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev), "device attribute");
+      if (major != 10)
+        return fail(W4B_CUDA, "libw4b200 is built for sm_100a only; device %d has compute capability %d.x", dev,
+                    major);
+      CUDA_TRY(cudaMalloc((void**)&c.status, sizeof(int)), "status word");
+      CUDA_TRY(cudaMemset(c.status, 0, sizeof(int)), "status word");
+      c.ready = true;
+    }
+  }
+  *out = &c;
+  return W4B_OK;
+}
+
+// ---- validation, in the reference's order (fused.cuh:175-193, mma.cuh:237-254) ----
+
+int check_w4(const w4b_packed_w4* p, const char* who) {
+  if (!p) INVALID("%s: null descriptor", who);
+  if (p->N < 1 || p->K < 1) INVALID("%s: bad dims", who);
+  if (p->gs < 8 || p->gs % 8 != 0) INVALID("%s: gs must be a multiple of 8", who);
+  if (p->G != (p->K + p->gs - 1) / p->gs) INVALID("%s: G inconsistent with K, gs", who);
+  if (!p->q || !p->scales) INVALID("%s: null pointer", who);
+  if (!p->symmetric && !p->zeros) INVALID("%s: asymmetric without zeros", who);
+  if (p->symmetric && p->zeros) INVALID("%s: symmetric carries no zeros", who);
+  return W4B_OK;
+}
+
+int check_mx(const w4b_packed_mx* p, const char* who) {  // mxfused.cuh:32-37
+  if (!p) INVALID("%s: null descriptor", who);
+  if (p->N < 1 || p->K < 1) INVALID("%s: bad dims", who);
+  if (p->B != (p->K + 31) / 32) INVALID("%s: B inconsistent with K", who);
+  if (!p->q || !p->scales) INVALID("%s: null pointer", who);
+  return W4B_OK;
+}
+
+// Which reference entry's launch bounds apply to a call (fused vs mma) and
+// which kernel serves it.
+int resolve_path(int path, int M) {
+  if (path == W4B_PATH_AUTO) return M < kMmaMinM ? W4B_PATH_STREAM : W4B_PATH_TENSOR;
+  return path;
+}
+
+int check_gemm_bounds(int N, int M, int entry, const char* who) {
+  if (M < 1) INVALID("%s: bad M", who);
+  if (entry == W4B_PATH_TENSOR) {  // mma.cuh:252-254
+    if (M > 65535 * 64 || N > INT_MAX - 64) INVALID("%s: launch grid out of range", who);
+  } else {  // fused.cuh:187-194
+    const int mtile = M <= 1 ? 1 : (M <= 2 ? 2 : 4);
+    const int rpw = M <= 4 ? 1 : 4;
+    if (M > 65535 * mtile || N > INT_MAX - 8 * rpw) INVALID("%s: launch grid out of range", who);
+  }
+  return W4B_OK;
+}
+
+// Chooses the kernel: the requested one when the shape fits it, else generic.
+// (The tensor kernel is served by the stream kernel's shape rules until it has
+// its own; both fall back to the generic kernel.)
+int route_kernel(int entry, int N, int K, int gs_or_0, const void* q, const void* scales, const void* x) {
+  if (entry == W4B_PATH_GENERIC) return W4B_PATH_GENERIC;
+  if (stream_gemm_supported(N, K, gs_or_0, q, scales, x)) return W4B_PATH_STREAM;
+  return W4B_PATH_GENERIC;
+}
+
+int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros, int N, int K, int G,
+             const void* x, void* c, int M, int entry, cudaStream_t stream, void* w_out, const char* who) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  const int kernel = route_kernel(entry, N, K, fmt == 2 ? 0 : gs, q, scales, x);
+  if (kernel == W4B_PATH_STREAM) {
+    StreamPlan plan;
+    stream_gemm_plan(N, K, M, ctx->sm_count, &plan);
+    CUDA_TRY(ctx->gemm_ws.reserve(plan.ws_bytes, false), "gemm workspace");
+    CUDA_TRY(ctx->gemm_counters.reserve(plan.counter_ints * sizeof(int), true), "gemm counters");
+    CUDA_TRY(stream_gemm_launch(fmt, gs, q, scales, zeros, N, K, G, (const __half*)x, (__half*)c, M,
+                                (__half*)w_out, plan, (float*)ctx->gemm_ws.ptr, (int*)ctx->gemm_counters.ptr,
+                                ctx->status, stream),
+             who);
+    g_launches += 1;
+    return W4B_OK;
+  }
+  CUDA_TRY(generic_gemm_launch(fmt, gs, q, scales, zeros, N, K, G, (const __half*)x, (__half*)c, M,
+                               (__half*)w_out, stream),
+           who);
+  g_launches += 1;
+  return W4B_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* w4b_last_error(void) { return g_err; }
+
+int w4b_dispatch_mma_min_m(void) { return kMmaMinM; }
+
+unsigned long long w4b_launch_count(void) { return g_launches.load(); }
+
+int w4b_device_status(void) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return -rc;
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    cuda_fail(cudaGetLastError(), "cudaDeviceSynchronize");
+    return -W4B_CUDA;
+  }
+  int st = 0;
+  if (cudaMemcpy(&st, ctx->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -W4B_CUDA;
+  if (st != 0) cudaMemset(ctx->status, 0, sizeof(int));
+  return st;
+}
+
+int w4b_gemm_w4_route(const w4b_packed_w4* p, int M, int path, const void* x) {
+  if (check_w4(p, "route") || M < 1) return -1;
+  return route_kernel(resolve_path(path, M), p->N, p->K, p->gs, p->q, p->scales, x);
+}
+
+int w4b_gemm_mx_route(const w4b_packed_mx* p, int M, int path, const void* x) {
+  if (check_mx(p, "route") || M < 1) return -1;
+  return route_kernel(resolve_path(path, M), p->N, p->K, 0, p->q, p->scales, x);
+}
+
+int w4b_gemm_w4(const w4b_packed_w4* p, const void* x, void* c, int M, int path, void* stream, void* w_out) {
+  if (path < W4B_PATH_AUTO || path > W4B_PATH_GENERIC) INVALID("gemm: unknown path %d", path);
+  if (int rc = check_w4(p, "gemm")) return rc;
+  if (!x || !c) INVALID("gemm: null pointer");
+  if (M < 1) INVALID("gemm: bad M");
+  const int entry = resolve_path(path, M);
+  if (int rc = check_gemm_bounds(p->N, M, entry, "gemm")) return rc;
+  return run_gemm(p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, x, c, M, entry,
+                  (cudaStream_t)stream, w_out, "gemm kernel");
+}
+
+int w4b_gemm_mx(const w4b_packed_mx* p, const void* x, void* c, int M, int path, void* stream, void* w_out) {
+  if (path < W4B_PATH_AUTO || path > W4B_PATH_GENERIC) INVALID("gemm_mx: unknown path %d", path);
+  if (int rc = check_mx(p, "gemm_mx")) return rc;
+  if (!x || !c) INVALID("gemm_mx: null pointer");
+  if (M < 1) INVALID("gemm_mx: bad M");
+  const int entry = resolve_path(path, M);
+  if (int rc = check_gemm_bounds(p->N, M, entry, "gemm_mx")) return rc;
+  return run_gemm(2, 32, p->q, p->scales, nullptr, p->N, p->K, p->B, x, c, M, entry, (cudaStream_t)stream, w_out,
+                  "gemm_mx kernel");
+}
+
+int w4b_gemm_w4_hostio(const w4b_packed_w4* p, const void* x_host, void* c_host, int M, int path, void* stream) {
+  if (path < W4B_PATH_AUTO || path > W4B_PATH_GENERIC) INVALID("gemm hostio: unknown path %d", path);
+  if (int rc = check_w4(p, "gemm hostio")) return rc;
+  if (!x_host || !c_host) INVALID("gemm hostio: null pointer");
+  if (M < 1) INVALID("gemm hostio: bad M");
+  const int entry = resolve_path(path, M);
+  if (int rc = check_gemm_bounds(p->N, M, entry, "gemm hostio")) return rc;
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  const size_t xb = (size_t)M * p->K * sizeof(__half), cb = (size_t)M * p->N * sizeof(__half);
+  CUDA_TRY(ctx->io_x.reserve(xb, false), "hostio x staging");
+  CUDA_TRY(ctx->io_c.reserve(cb, false), "hostio c staging");
+  cudaStream_t st = (cudaStream_t)stream;
+  CUDA_TRY(cudaMemcpyAsync(ctx->io_x.ptr, x_host, xb, cudaMemcpyHostToDevice, st), "hostio h2d");
+  if (int rc = run_gemm(p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, ctx->io_x.ptr,
+                        ctx->io_c.ptr, M, entry, st, nullptr, "gemm kernel"))
+    return rc;
+  CUDA_TRY(cudaMemcpyAsync(c_host, ctx->io_c.ptr, cb, cudaMemcpyDeviceToHost, st), "hostio d2h");
+  CUDA_TRY(cudaStreamSynchronize(st), "hostio sync");
+  return W4B_OK;
+}
+
+int w4b_dequant_w4(const w4b_packed_w4* p, void* w, void* stream) {
+  // dequant.cuh:62-82 (null check precedes the mode checks there)
+  if (!p) INVALID("dequant: null descriptor");
+  if (p->N < 1 || p->K < 1) INVALID("dequant: bad dims");
+  if (p->gs < 8 || p->gs % 8 != 0) INVALID("dequant: gs must be a multiple of 8");
+  if (p->G != (p->K + p->gs - 1) / p->gs) INVALID("dequant: G inconsistent with K, gs");
+  if (!p->q || !p->scales || !w) INVALID("dequant: null pointer");
+  if (!p->symmetric && !p->zeros) INVALID("dequant: asymmetric without zeros");
+  if (p->symmetric && p->zeros) INVALID("dequant: symmetric carries no zeros");
+  if ((long long)p->N * words(p->K) >= (1LL << 31)) INVALID("dequant: N*words(K) exceeds 2^31");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(dequant_w4_launch(p->q, (const __half*)p->scales, p->zeros, p->N, p->K, p->gs, p->G, p->symmetric,
+                             (__half*)w, (cudaStream_t)stream),
+           "dequant kernel");
+  g_launches += 1;
+  return W4B_OK;
+}
+
+int w4b_dequant_mx(const w4b_packed_mx* p, void* w, void* stream) {
+  if (int rc = check_mx(p, "mx dequant")) return rc;  // mxfused.cuh:57-69
+  if (!w) INVALID("mx dequant: null output");
+  if ((long long)p->N * words(p->K) >= (1LL << 31)) INVALID("mx dequant: N*words(K) exceeds 2^31");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(dequant_mx_launch(p->q, p->scales, p->N, p->K, p->B, (__half*)w, (cudaStream_t)stream),
+           "mx dequant kernel");
+  g_launches += 1;
+  return W4B_OK;
+}
+
+int w4b_dequant_f8(const uint8_t* q, const uint16_t* s, void* w, int S, int D, int gs, void* stream) {
+  // kvflash.cuh:435-457
+  if (S < 1 || D < 1) INVALID("f8 dequant: bad dims");
+  if (gs < 8 || gs % 8 != 0) INVALID("f8 dequant: gs must be a multiple of 8");
+  if (!q || !s || !w) INVALID("f8 dequant: null pointer");
+  if ((long long)S * ((D + 3) / 4) >= (1LL << 31)) INVALID("f8 dequant: S*words4(D) exceeds 2^31");
+  if (D % 4 != 0) INVALID("f8 dequant: D must be a multiple of 4");
+  if ((uintptr_t)q % 4 != 0) INVALID("f8 dequant: q must be 4-byte aligned");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(dequant_f8_launch(q, (const __half*)s, (__half*)w, S, D, gs, (cudaStream_t)stream), "f8 dequant kernel");
+  g_launches += 1;
+  return W4B_OK;
+}
+
+// ---- decode attention ------------------------------------------------------
+
+namespace {
+
+constexpr int kKvMaxS = 4096;      // kvattention.cuh:36 (single-block entries only)
+constexpr int kKvMaxD = 512;       // kvattention.cuh:37
+constexpr int kFlashTile = 256;    // kvflash.cuh:35: bounds S through the reference's grid.y
+
+int check_kv_w4(const w4b_kv_w4* p, bool single, const char* who) {  // kvattention.cuh:50-67, kvflash.cuh:37-54
+  if (!p) INVALID("%s: null descriptor", who);
+  if (p->H < 1 || p->S < 1 || p->D < 1) INVALID("%s: bad dims", who);
+  if (single && p->S > kKvMaxS) INVALID("%s: S exceeds the shared-memory bound", who);
+  if (p->D > kKvMaxD) INVALID("%s: D exceeds the shared-memory bound", who);
+  if (p->gs < 8 || p->gs % 8 != 0) INVALID("%s: gs must be a multiple of 8", who);
+  if (p->G != (p->D + p->gs - 1) / p->gs) INVALID("%s: G inconsistent with D, gs", who);
+  if (!p->q_k || !p->s_k || !p->q_v || !p->s_v) INVALID("%s: null pointer", who);
+  if (!p->symmetric && (!p->z_k || !p->z_v)) INVALID("%s: asymmetric without zeros", who);
+  if (p->symmetric && (p->z_k || p->z_v)) INVALID("%s: symmetric carries no zeros", who);
+  if (!single && p->S > 65535 * kFlashTile) INVALID("%s: S exceeds the tile-grid bound", who);
+  return W4B_OK;
+}
+
+int run_attn(const AttnSource& src, const void* q, void* out, int H, int S, int D, cudaStream_t stream,
+             void* k_out, void* v_out, const char* who) {
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  const int splits = attn_flash_splits(H, S, ctx->sm_count);
+  CUDA_TRY(ctx->attn_ws.reserve(attn_flash_ws_bytes(H, D, splits), false), "attention workspace");
+  int launches = 0;
+  CUDA_TRY(attn_flash_launch(src, (const __half*)q, (__half*)out, H, S, D, splits, (float*)ctx->attn_ws.ptr,
+                             (__half*)k_out, (__half*)v_out, stream, &launches),
+           who);
+  g_launches += (unsigned long long)launches;
+  return W4B_OK;
+}
+
+AttnSource w4_source(const w4b_kv_w4* p) {
+  AttnSource s;
+  memset(&s, 0, sizeof(s));
+  s.fmt = p->symmetric ? ATTN_W4_SYM : ATTN_W4_ASYM;
+  s.k = p->q_k;
+  s.v = p->q_v;
+  s.s_k = (const __half*)p->s_k;
+  s.s_v = (const __half*)p->s_v;
+  s.z_k = p->z_k;
+  s.z_v = p->z_v;
+  s.gs = p->gs;
+  s.G = p->G;
+  s.slab_rows = p->S;
+  return s;
+}
+
+int fp16_attn(const void* q, const void* k16, const void* v16, void* out, int H, int S, int D, void* stream,
+              bool single, const char* who) {
+  if (H < 1 || S < 1 || D < 1) INVALID("%s: bad dims", who);  // kvflash.cuh:368-377, kvattention.cuh:229-236
+  if (single && S > kKvMaxS) INVALID("%s: S exceeds the shared-memory bound", who);
+  if (D > kKvMaxD) INVALID("%s: D exceeds the shared-memory bound", who);
+  if (!single && S > 65535 * kFlashTile) INVALID("%s: S exceeds the tile-grid bound", who);
+  if (!q || !k16 || !v16 || !out) INVALID("%s: null pointer", who);
+  AttnSource s;
+  memset(&s, 0, sizeof(s));
+  s.fmt = ATTN_FP16;
+  s.k = k16;
+  s.v = v16;
+  s.slab_rows = S;
+  return run_attn(s, q, out, H, S, D, (cudaStream_t)stream, nullptr, nullptr, who);
+}
+
+}  // namespace
+
+int w4b_attn_flash_fp16(const void* q, const void* k16, const void* v16, void* out, int H, int S, int D,
+                        void* stream) {
+  return fp16_attn(q, k16, v16, out, H, S, D, stream, false, "kv flash fp16");
+}
+
+int w4b_attn_single_fp16(const void* q, const void* k16, const void* v16, void* out, int H, int S, int D,
+                         void* stream) {
+  return fp16_attn(q, k16, v16, out, H, S, D, stream, true, "kv fp16");
+}
+
+int w4b_attn_flash_w4(const w4b_kv_w4* p, const void* q, void* out, void* stream, void* k_out, void* v_out) {
+  if (int rc = check_kv_w4(p, false, "kv flash")) return rc;
+  if (!q || !out) INVALID("kv flash w4: null pointer");
+  return run_attn(w4_source(p), q, out, p->H, p->S, p->D, (cudaStream_t)stream, k_out, v_out, "kv flash w4");
+}
+
+int w4b_attn_single_w4(const w4b_kv_w4* p, const void* q, void* out, void* stream, void* k_out, void* v_out) {
+  if (int rc = check_kv_w4(p, true, "kv")) return rc;
+  if (!q || !out) INVALID("kv w4: null pointer");
+  return run_attn(w4_source(p), q, out, p->H, p->S, p->D, (cudaStream_t)stream, k_out, v_out, "kv w4");
+}
+
+int w4b_attn_flash_f8(const w4b_kv_f8* p, const void* q, void* out, void* stream, void* k_out, void* v_out) {
+  // kvflash.cuh:398-411,572-582
+  if (!p) INVALID("kv f8 flash: null descriptor");
+  if (p->H < 1 || p->S < 1 || p->D < 1) INVALID("kv f8 flash: bad dims");
+  if (p->D > kKvMaxD) INVALID("kv f8 flash: D exceeds the shared bound");
+  if (p->gs < 8 || p->gs % 8 != 0) INVALID("kv f8 flash: gs must be a multiple of 8");
+  if (p->G != (p->D + p->gs - 1) / p->gs) INVALID("kv f8 flash: G inconsistent with D, gs");
+  if (!p->q_k || !p->s_k || !p->q_v || !p->s_v) INVALID("kv f8 flash: null pointer");
+  if (p->S > 65535 * kFlashTile) INVALID("kv f8 flash: S exceeds the tile-grid bound");
+  if (!q || !out) INVALID("kv f8 flash: null io pointer");
+  if (p->D % 4 != 0) INVALID("kv f8 flash: D must be a multiple of 4");
+  if ((uintptr_t)p->q_k % 4 != 0 || (uintptr_t)p->q_v % 4 != 0) INVALID("kv f8 flash: cache bases 4-byte aligned");
+  if ((long long)p->S * ((p->D + 3) / 4) >= (1LL << 31)) INVALID("kv f8 flash: S*words4(D) exceeds 2^31");
+  AttnSource s;
+  memset(&s, 0, sizeof(s));
+  s.fmt = ATTN_F8;
+  s.k = p->q_k;
+  s.v = p->q_v;
+  s.s_k = (const __half*)p->s_k;
+  s.s_v = (const __half*)p->s_v;
+  s.gs = p->gs;
+  s.G = p->G;
+  s.slab_rows = p->S;
+  return run_attn(s, q, out, p->H, p->S, p->D, (cudaStream_t)stream, k_out, v_out, "kv f8 flash");
+}
+
+int w4b_attn_flash_w4_paged(const w4b_kv_w4* p, const int* bt, int page, int npages, const void* q, void* out,
+                            void* stream, void* k_out, void* v_out) {
+  // kvflash.cuh:733-754
+  if (!p) INVALID("kv paged flash: null descriptor");
+  if (p->H < 1 || p->S < 1 || p->D < 1) INVALID("kv paged flash: bad dims");
+  if (p->D > kKvMaxD) INVALID("kv paged flash: D exceeds the shared bound");
+  if (p->gs < 8 || p->gs % 8 != 0) INVALID("kv paged flash: gs must be a multiple of 8");
+  if (p->G != (p->D + p->gs - 1) / p->gs) INVALID("kv paged flash: G inconsistent with D, gs");
+  if (!p->q_k || !p->s_k || !p->q_v || !p->s_v || !bt) INVALID("kv paged flash: null pointer");
+  if (!p->symmetric && (!p->z_k || !p->z_v)) INVALID("kv paged flash: asymmetric without zeros");
+  if (p->symmetric && (p->z_k || p->z_v)) INVALID("kv paged flash: symmetric carries zeros");
+  if (page < 1 || npages < 1 || (unsigned long long)npages * (unsigned long long)page < (unsigned long long)p->S)
+    INVALID("kv paged flash: bad page geometry");
+  if ((long long)npages * page >= (1LL << 31)) INVALID("kv paged flash: pool rows exceed 2^31");
+  if (p->S > 65535 * kFlashTile) INVALID("kv paged flash: S exceeds tile-grid bound");
+  if (!q || !out) INVALID("kv paged flash: null io");
+  AttnSource s = w4_source(p);
+  s.bt = bt;
+  s.page = page;
+  s.slab_rows = (long long)npages * page;
+  return run_attn(s, q, out, p->H, p->S, p->D, (cudaStream_t)stream, k_out, v_out, "kv paged flash");
+}
+
+}  // extern "C"

@@ -1,0 +1,73 @@
+// Host-callable launchers of the CUDA kernels (one translation unit each).
+// Internal to libw4b200; the public surface is include/w4b_abi.h.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace w4b {
+
+// 32-bit words that hold n 4-bit codes (the reference's words(), include/w4/pack.hpp:33).
+__host__ __device__ __forceinline__ int words(int n) { return (n + 7) >> 3; }
+
+// ---- dequant.cu -----------------------------------------------------------
+cudaError_t dequant_w4_launch(const uint32_t* q, const __half* scales, const uint32_t* zeros, int N, int K,
+                              int gs, int G, int symmetric, __half* w, cudaStream_t stream);
+cudaError_t dequant_mx_launch(const uint32_t* q, const uint8_t* scales, int N, int K, int B, __half* w,
+                              cudaStream_t stream);
+cudaError_t dequant_f8_launch(const uint8_t* q, const __half* s, __half* w, int S, int D, int gs,
+                              cudaStream_t stream);
+
+// ---- gemm_generic.cu --------------------------------------------------------
+// fmt: 0 = W4 symmetric, 1 = W4 asymmetric, 2 = MXFP4 (gs ignored, G = blocks per row).
+cudaError_t generic_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
+                                int N, int K, int G, const __half* x, __half* c, int M, __half* w_out,
+                                cudaStream_t stream);
+
+// ---- gemm_stream.cu ---------------------------------------------------------
+struct StreamPlan {
+  int rows_per_pass;  // activation rows resident in shared memory per pass
+  int mt;             // 8-row m-tiles per pass (1 or 2)
+  int passes;         // grid.y
+  int stages;         // ring depth
+  int P, C;           // panels of 128 rows, chunks of 256 k
+  long long U;        // work units
+  int grid_x;         // persistent CTAs
+  int xpitch;
+  size_t smem;
+  size_t ws_bytes;      // FP32 partial-fragment slots
+  size_t counter_ints;  // per-(pass, tile) arrival counters, zero between launches
+};
+bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, const void* scales,
+                           const void* x);
+void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan);
+cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
+                               int N, int K, int G, const __half* x, __half* c, int M, __half* w_out,
+                               const StreamPlan& plan, float* ws, int* counters, int* status,
+                               cudaStream_t stream);
+
+// ---- attn_flash.cu ----------------------------------------------------------
+enum : int { ATTN_FP16 = 0, ATTN_W4_SYM = 1, ATTN_W4_ASYM = 2, ATTN_F8 = 3 };
+// Where the K / V rows of one call live. Head h owns rows [h*slab_rows, (h+1)*slab_rows)
+// of every array; logical position t is row t, or bt[t/page]*page + t%page when bt != null.
+struct AttnSource {
+  int fmt;
+  const void* k;        // FP16: halves [rows][D]; W4: uint32 [rows][words(D)]; F8: bytes [rows][D]
+  const void* v;
+  const __half* s_k;    // W4 / F8: [rows][G]
+  const __half* s_v;
+  const uint32_t* z_k;  // W4 asymmetric: [rows][words(G)]
+  const uint32_t* z_v;
+  int gs, G;
+  const int* bt;
+  int page;
+  long long slab_rows;
+};
+int attn_flash_splits(int H, int S, int sm_count);
+size_t attn_flash_ws_bytes(int H, int D, int splits);
+cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
+                              float* ws, __half* k_out, __half* v_out, cudaStream_t stream, int* launches);
+
+}  // namespace w4b
