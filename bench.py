@@ -172,6 +172,14 @@ def run_mine(args):
     if status != 0 or not rel <= 1e-3:
         raise SystemExit(f"bench: parity check failed (rel L2 {rel:.3e}, device status {status})")
 
+    if args.profile:
+        # profiling target (run under ncu on one GPU): a few eager launches of the headline GEMM, nothing else
+        for i in range(max(args.warmup, 3) + args.steps):
+            step(i)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": True, "launches": w4.launch_count(), "workload": WORKLOAD}))
+        return
+
     clocks = Clocks(local)
     if rank == 0:
         clocks.start()
@@ -488,6 +496,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="mine", choices=["mine", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="run warmup + steps eager launches of the headline GEMM and exit (ncu target)")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = 20000 if args.impl == "mine" else 50

@@ -50,12 +50,13 @@ def test_w4_attention(oracle, name, i, cfg, sym):
         assert np.array_equal(bits(out), bits(out2))
     # FP16 cache holding the dequantised values: same reference (tests/test_gpu.cu:700-781)
     out = empty_f16(H * D)
-    w4.attention_fp16_flash(ptr(q_d), ptr(dev(kd)), ptr(dev(vd)), ptr(out), H, S, D)
+    kd_d, vd_d = dev(kd), dev(vd)  # keep the device buffers alive across the launches
+    w4.attention_fp16_flash(ptr(q_d), ptr(kd_d), ptr(vd_d), ptr(out), H, S, D)
     sync_ok()
     assert cases.rel_l2(cases.f16(bits(out)), ref) <= TOL
     if S <= 4096:
         out1 = empty_f16(H * D)
-        w4.attention_fp16(ptr(q_d), ptr(dev(kd)), ptr(dev(vd)), ptr(out1), H, S, D)
+        w4.attention_fp16(ptr(q_d), ptr(kd_d), ptr(vd_d), ptr(out1), H, S, D)
         sync_ok()
         assert cases.rel_l2(cases.f16(bits(out1)), ref) <= TOL
 
@@ -134,7 +135,8 @@ def test_baseline_c4_shape(oracle, fmt):
     q_d, out = dev(q), empty_f16(H * D)
     if fmt == "fp16":
         kd, vd = k.astype(np.float16).view(np.uint16), v.astype(np.float16).view(np.uint16)
-        w4.attention_fp16_flash(ptr(q_d), ptr(dev(kd)), ptr(dev(vd)), ptr(out), H, S, D)
+        kd_d, vd_d = dev(kd), dev(vd)
+        w4.attention_fp16_flash(ptr(q_d), ptr(kd_d), ptr(vd_d), ptr(out), H, S, D)
     elif fmt == "w4":
         c = oracle.quantize_cache_w4(k, v, H, S, D, gs, True)
         kd, vd = oracle.dequant_cache_w4(c, "k"), oracle.dequant_cache_w4(c, "v")

@@ -116,13 +116,15 @@ def test_linearity_at_full_size(oracle):
     xs = (x1.astype(np.float32) + x2.astype(np.float32)).astype(np.float16)
     outs = []
     for x in (x1, x2, xs):
-        c, _ = run_entry(w4.gemm, wts.desc, dev(x.view(np.uint16)), 1, N, K, False)
+        x_d = dev(x.view(np.uint16))
+        c, _ = run_entry(w4.gemm, wts.desc, x_d, 1, N, K, False)
         outs.append(cases.f16(c))
     # x1 + x2 was rounded to FP16 once more than the two separate products
     assert cases.rel_l2(outs[2], outs[0] + outs[1]) <= 2e-3
     w_out = empty_f16(N * K)
     c = empty_f16(N)
-    w4.gemm(wts.desc, ptr(dev(x1.view(np.uint16))), ptr(c), 1, None, ptr(w_out))
+    x_d = dev(x1.view(np.uint16))
+    w4.gemm(wts.desc, ptr(x_d), ptr(c), 1, None, ptr(w_out))
     sync_ok()
     assert np.array_equal(bits(w_out), oracle.dequant_all_w4(p))
 
@@ -138,7 +140,8 @@ def test_baseline_c2_against_oracle(oracle, N, K, M):
         _C2[key] = (p, oracle.dequant_all_w4(p), W4Weights(p))
     p, wd, wts = _C2[key]
     x = oracle.normal_f16(M * K, 1 + M)
-    c, _ = run_entry(w4.gemm, wts.desc, dev(x), M, N, K, False)
+    x_d = dev(x)
+    c, _ = run_entry(w4.gemm, wts.desc, x_d, M, N, K, False)
     ref = oracle.gemm_oracle(x, M, K, wd, N, threads=os.cpu_count() or 8)
     assert cases.rel_l2(cases.f16(c), ref) <= TOL
 
@@ -152,7 +155,8 @@ def test_baseline_c2_ragged_k(oracle):
     p = oracle.quantize_w4(oracle.normal_f64(N * K, 3) * 0.02, N, K, gs, False)
     wd, wts = oracle.dequant_all_w4(p), W4Weights(p)
     x = oracle.normal_f16(M * K, 4)
-    c, w_hook = run_entry(w4.gemm, wts.desc, dev(x), M, N, K, True)
+    x_d = dev(x)
+    c, w_hook = run_entry(w4.gemm, wts.desc, x_d, M, N, K, True)
     assert np.array_equal(w_hook, wd)
     assert cases.rel_l2(cases.f16(c), oracle.gemm_oracle(x, M, K, wd, N, threads=8)) <= TOL
 
@@ -164,7 +168,8 @@ def test_baseline_c3_partial_blocks(oracle, K):
     p = oracle.quantize_mx(oracle.normal_f64(N * K, K) * 0.02, N, K)
     wd, wts = oracle.dequant_all_mx(p), MxWeights(p)
     x = oracle.normal_f16(M * K, K + 1)
-    c, w_hook = run_entry(w4.gemm_mx, wts.desc, dev(x), M, N, K, True)
+    x_d = dev(x)
+    c, w_hook = run_entry(w4.gemm_mx, wts.desc, x_d, M, N, K, True)
     assert np.array_equal(w_hook, wd)
     assert cases.rel_l2(cases.f16(c), oracle.gemm_oracle(x, M, K, wd, N)) <= TOL
 
@@ -176,7 +181,8 @@ def test_baseline_c3_mx_8192(oracle, M):
         p = oracle.quantize_mx(oracle.normal_f64(N * K, 0) * 0.02, N, K)
         _C3.update(p=p, wd=oracle.dequant_all_mx(p), wts=MxWeights(p))
     x = oracle.normal_f16(M * K, 1 + M)
-    c, _ = run_entry(w4.gemm_mx, _C3["wts"].desc, dev(x), M, N, K, False)
+    x_d = dev(x)
+    c, _ = run_entry(w4.gemm_mx, _C3["wts"].desc, x_d, M, N, K, False)
     ref = oracle.gemm_oracle(x, M, K, _C3["wd"], N, threads=os.cpu_count() or 8)
     assert cases.rel_l2(cases.f16(c), ref) <= TOL
 
@@ -191,7 +197,8 @@ def test_hostio_entry(oracle):
     p = oracle.quantize_w4(oracle.normal_f64(N * K, 9) * 0.02, N, K, 128, True)
     wts = W4Weights(p)
     x = oracle.normal_f16(M * K, 10)
-    c_dev, _ = run_entry(w4.gemm, wts.desc, dev(x), M, N, K, False)
+    x_d = dev(x)
+    c_dev, _ = run_entry(w4.gemm, wts.desc, x_d, M, N, K, False)
     xh = torch.from_numpy(x.view(np.int16).copy()).pin_memory()
     ch = torch.empty(M * N, dtype=torch.int16).pin_memory()
     w4.gemm_hostio(wts.desc, xh.data_ptr(), ch.data_ptr(), M)
