@@ -6,30 +6,38 @@
 // read from HBM exactly once, and the kernel is organised so that this stream
 // never stalls.
 //
-//  * Work unit = 128 rows x 256 k of packed codes = one 16 KB 2-D TMA box
-//    (cp.async.bulk.tensor, 128-byte swizzle, no multicast). The units of the
-//    whole matrix are numbered panel-major / chunk-fastest and cut into equal
-//    contiguous ranges, one per persistent CTA (one CTA per SM), so all SMs
-//    finish together whatever N and K are ("stream-K").
-//  * Warp 8 is the producer: per unit it issues the TMA box plus 4..16-byte
-//    cp.async copies of the unit's scales / zero words into a ring of up to 12
-//    stages; full/empty mbarriers hand stages over. With ~200 KB of ring per SM
-//    the loads of a CTA's whole share are in flight almost from the start.
-//  * Warps 0..7 are consumers; warp w owns rows 16w..16w+15 of every unit. A
-//    lane decodes packed words in registers (w4b_common.cuh: no tables, no
-//    local memory) straight into mma.sync m16n8k16 A fragments; the activations
-//    sit in shared memory, pre-arranged once per CTA in the decoder's pairing,
-//    and are the B fragments; FP32 accumulators live in registers across the
-//    units of a panel. At M = 1 the budget is ~2.8 issue slots per weight at
-//    full HBM rate, which rules out per-weight FP32 FMAs: the contraction has
-//    to ride the tensor pipe even though the kernel is bandwidth-bound.
-//  * A panel whose K range is split between CTAs is finished deterministically:
-//    every contributor parks its FP32 fragment in a workspace slot and bumps
-//    the tile's counter; the last arriver adds the slots in CTA order (never
-//    in arrival order) and writes FP16. Outputs are therefore bit-identical
-//    from run to run.
+//  * Work unit = 64 rows x 256 k of packed codes = one 8 KB 2-D TMA box
+//    (cp.async.bulk.tensor, 128-byte swizzle, no multicast). A "panel" is the
+//    C = K/256 units of 64 rows. The units of the whole matrix are numbered
+//    panel-major / chunk-fastest and cut into equal contiguous ranges, one per
+//    persistent CTA (one CTA per SM), so all SMs finish together whatever N and
+//    K are ("stream-K").
+//  * Warp 16 is the producer: per unit it issues the TMA box plus 4..16-byte
+//    cp.async copies of the unit's scales / zero words into a ring of up to 22
+//    stages; full/empty mbarriers hand stages over, so ~200 KB per SM are in
+//    flight from the first microsecond.
+//  * Warps 0..15 are consumers: warp w owns the 16-row tile (w & 3) of every
+//    fourth unit (phase w >> 2), which keeps four stages under computation at a
+//    time. A lane decodes packed words in registers (w4b_common.cuh: no tables,
+//    no local memory) straight into mma.sync m16n8k16 A fragments; the
+//    activations sit in shared memory, arranged once per CTA in the decoder's
+//    pairing, and are the B fragments; FP32 accumulators stay in registers
+//    across the units of a panel. On B200 the packed-half pipe issues 64 lanes
+//    per clock per SM, so the 8 half2 operations a word needs already cost 16
+//    pipe cycles per warp-word: there is no room for per-weight FP32 FMAs, and
+//    the contraction rides the tensor pipe although the kernel is
+//    bandwidth-bound.
+//  * Leaving a panel, the four phase warps of a tile add their fragments in
+//    shared memory in phase order. A panel whose K range is shared by several
+//    CTAs is finished by the CTA that owns the panel's END: the others park
+//    their FP32 fragment in a workspace slot and bump the tile's counter; the
+//    owner waits (bounded) for the counter and adds the slots in CTA order.
+//    Every CTA walks its range as [tail part, whole panels, head part], so what
+//    others wait for is produced first and what a CTA waits for is consumed
+//    last: in the common case nobody waits, and the order of the additions
+//    never depends on timing - outputs are bit-identical from run to run.
 //
-// Shapes served: K % 256 == 0, N >= 128, W4 group size 32 / 64 / 128 (MXFP4:
+// Shapes served: K % 256 == 0, N >= 64, W4 group size 32 / 64 / 128 (MXFP4:
 // its fixed 32-element blocks), 16-byte aligned q / scales / x. Anything else
 // is routed to the generic kernel by the dispatcher.
 #include <cuda.h>
@@ -41,14 +49,19 @@ namespace w4b {
 
 namespace {
 
-constexpr int SK_ROWS = 128;
-constexpr int SK_KC = 256;
-constexpr int SK_STAGE_Q = SK_ROWS * SK_KC / 2;  // 16384 bytes of codes per unit
+constexpr int SK_ROWS = 64;                     // rows per unit: 4 tiles of 16
+constexpr int SK_KC = 256;                      // k per unit
+constexpr int SK_STAGE_Q = SK_ROWS * SK_KC / 2;  // 8192 bytes of codes per unit
 constexpr int SK_META_SCALES = SK_ROWS * 16;     // <= 8 FP16 scales or 8 E8M0 bytes per row
 constexpr int SK_META = SK_META_SCALES + SK_ROWS * 4;  // + one zero word per row
-constexpr int SK_CONSUMERS = 8;
+constexpr int SK_TILES = 4;
+constexpr int SK_PHASES = 4;
+constexpr int SK_CONSUMERS = SK_TILES * SK_PHASES;
 constexpr int SK_THREADS = 32 * (SK_CONSUMERS + 1);
-constexpr int SK_MAX_STAGES = 12;
+constexpr int SK_MAX_STAGES = 22;
+constexpr int SK_BURST = 4;  // units the producer issues back to back
+constexpr int SK_BAR_BYTES = 2 * 8 * SK_MAX_STAGES;
+constexpr int SK_RED_BYTES_PER_MT = SK_TILES * (SK_PHASES - 1) * 32 * 16;  // cross-phase exchange
 
 enum : int { F_W4_SYM = 0, F_W4_ASYM = 1, F_MX = 2 };
 
@@ -60,18 +73,18 @@ struct StreamParams {
   __half* c;
   __half* w_out;
   int N, K, M;
-  int G;       // scales per row: groups (W4) or 32-blocks (MX)
-  int C, P;    // 256-k chunks per row, 128-row panels
-  long long U; // units = P * C
+  int G;        // scales per row: groups (W4) or 32-blocks (MX)
+  int C, P;     // 256-k chunks per row, 64-row panels
+  long long U;  // units = P * C
   int stages;
-  int xrows;   // activation rows per pass (<= 8*MT); pass y covers rows y*xrows ...
-  int xpitch;  // bytes between activation rows in shared memory (== 64 mod 128)
+  int xrows;    // activation rows per pass (<= 8*MT); pass y covers rows y*xrows ...
+  int xpitch;   // bytes between activation rows in shared memory (== 64 mod 128)
   float* ws;
   int* counters;
   int* status;
 };
 
-__device__ __forceinline__ long long unit_begin(long long U, int b, int grid) {
+__host__ __device__ __forceinline__ long long unit_begin(long long U, int b, int grid) {
   return U * (long long)b / grid;
 }
 // The CTA whose range holds unit t (ranges are [U*b/grid, U*(b+1)/grid)).
@@ -79,64 +92,97 @@ __device__ __forceinline__ int unit_owner(long long U, long long t, int grid) {
   return (int)(((t + 1) * grid + U - 1) / U) - 1;
 }
 
+// The order in which a CTA walks its range [u0, u1): the part of the last panel
+// (whose end another CTA owns) first, then the whole panels, then the part of
+// the first panel (whose end this CTA owns). A range inside one panel is one
+// segment.
+struct Walk {
+  long long u0, u1, pb, pe;
+  int len_tail, n_full, len_head, nseg;
+  bool single;
+  __device__ Walk(long long a, long long b, int C) : u0(a), u1(b) {
+    pb = (u0 + C - 1) / C * C;  // first panel boundary at or after u0
+    pe = u1 / C * C;            // last panel boundary at or before u1
+    single = pb > pe;           // no boundary inside [u0, u1]: the range lies within one panel
+    if (single) {
+      len_tail = n_full = 0;
+      len_head = (int)(u1 - u0);
+      nseg = 1;
+    } else {
+      len_tail = (int)(u1 - pe);
+      n_full = (int)((pe - pb) / C);
+      len_head = (int)(pb - u0);
+      nseg = (len_tail > 0) + n_full + (len_head > 0);
+    }
+  }
+  // segment i -> first unit and length (all units of a segment lie in one panel)
+  __device__ void segment(int i, int C, long long* ua, int* len) const {
+    if (single) {
+      *ua = u0;
+      *len = len_head;
+      return;
+    }
+    if (len_tail > 0) {
+      if (i == 0) {
+        *ua = pe;
+        *len = len_tail;
+        return;
+      }
+      --i;
+    }
+    if (i < n_full) {
+      *ua = pb + (long long)i * C;
+      *len = C;
+      return;
+    }
+    *ua = u0;
+    *len = len_head;
+  }
+};
+
 template <int FMT, int GS>
 struct Groups;  // per-row decode constants of one unit: [0] for words 0-3, [1] for words 4-7
 
 template <int GS>
 struct Groups<F_W4_SYM, GS> {
   W4Group g[2];
-  __device__ __forceinline__ void load(uint32_t meta_row, uint32_t /*zero_row*/, int c, int /*ch*/) {
+  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* /*zero_row*/, int c, int /*ch*/) {
     constexpr int NGU = SK_KC / GS;
     const int gi = GS == 128 ? (c >> 1) : (GS == 64 ? c : 2 * c);
-    unsigned short s0, s1;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s0) : "r"(meta_row + 2 * gi));
-    g[0] = w4_group(__ushort_as_half(s0), 8u);
-    if (NGU == 8) {
-      asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s1) : "r"(meta_row + 2 * gi + 2));
-      g[1] = w4_group(__ushort_as_half(s1), 8u);
-    } else {
-      g[1] = g[0];
-    }
+    const __half* sc = reinterpret_cast<const __half*>(meta_row);
+    g[0] = w4_group(sc[gi], 8u);
+    g[1] = NGU == 8 ? w4_group(sc[gi + (NGU == 8 ? 1 : 0)], 8u) : g[0];
   }
-  __device__ __forceinline__ void decode(uint32_t w, int half, __half2 out[4]) const {
-    dq_w4_word(w, g[half], out);
+  __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts& k, __half2 out[4]) const {
+    dq_w4_word(w, g[half], k, out);
   }
 };
 
 template <int GS>
 struct Groups<F_W4_ASYM, GS> {
   W4Group g[2];
-  __device__ __forceinline__ void load(uint32_t meta_row, uint32_t zero_row, int c, int ch) {
+  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* zero_row, int c, int ch) {
     constexpr int NGU = SK_KC / GS;
     const int gi = GS == 128 ? (c >> 1) : (GS == 64 ? c : 2 * c);
-    unsigned short s0, s1;
-    uint32_t zw;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s0) : "r"(meta_row + 2 * gi));
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(zw) : "r"(zero_row));
+    const __half* sc = reinterpret_cast<const __half*>(meta_row);
+    const uint32_t zw = *reinterpret_cast<const uint32_t*>(zero_row);
     const int nib = (ch * NGU + gi) & 7;  // group index within its zero word
-    g[0] = w4_group(__ushort_as_half(s0), (zw >> (4 * nib)) & 0xFu);
-    if (NGU == 8) {
-      asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s1) : "r"(meta_row + 2 * gi + 2));
-      g[1] = w4_group(__ushort_as_half(s1), (zw >> (4 * nib + 4)) & 0xFu);
-    } else {
-      g[1] = g[0];
-    }
+    g[0] = w4_group(sc[gi], (zw >> (4 * nib)) & 0xFu);
+    g[1] = NGU == 8 ? w4_group(sc[gi + (NGU == 8 ? 1 : 0)], (zw >> (4 * nib + 4)) & 0xFu) : g[0];
   }
-  __device__ __forceinline__ void decode(uint32_t w, int half, __half2 out[4]) const {
-    dq_w4_word(w, g[half], out);
+  __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts& k, __half2 out[4]) const {
+    dq_w4_word(w, g[half], k, out);
   }
 };
 
 template <int GS>
 struct Groups<F_MX, GS> {
   MxBlock b[2];
-  __device__ __forceinline__ void load(uint32_t meta_row, uint32_t /*zero_row*/, int c, int /*ch*/) {
-    unsigned short s;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s) : "r"(meta_row + 2 * c));
-    b[0] = mx_block((uint32_t)s & 0xFFu);
-    b[1] = mx_block((uint32_t)s >> 8);
+  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* /*zero_row*/, int c, int /*ch*/) {
+    b[0] = mx_block(meta_row[2 * c]);
+    b[1] = mx_block(meta_row[2 * c + 1]);
   }
-  __device__ __forceinline__ void decode(uint32_t w, int half, __half2 out[4]) const {
+  __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts&, __half2 out[4]) const {
     dq_mx_word(w, b[half], out);
   }
 };
@@ -154,30 +200,36 @@ __device__ __forceinline__ uint32_t word_of(const uint4& a, const uint4& b, int 
   }
 }
 
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 template <int FMT, int GS, int MT, bool HOOK>
 __global__ void __launch_bounds__(SK_THREADS, 1)
     stream_gemm_kernel(const __grid_constant__ CUtensorMap tmap, const StreamParams a) {
-  extern __shared__ __align__(1024) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
   const int stages = a.stages;
-  const uint32_t sm_q = (smem_u32(smem) + 1023u) & ~1023u;  // the swizzle pattern repeats every 1024 bytes
-  const uint32_t sm_meta = sm_q + (uint32_t)stages * SK_STAGE_Q;
-  const uint32_t sm_x = sm_meta + (uint32_t)stages * SK_META;
-  const uint32_t sm_bar = sm_x + (uint32_t)a.xrows * (uint32_t)a.xpitch;
+  // the swizzle pattern repeats every 1024 bytes: align the ring to it
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sm_q = smem;
+  uint8_t* sm_meta = sm_q + (size_t)stages * SK_STAGE_Q;
+  uint8_t* sm_x = sm_meta + (size_t)stages * SK_META;
+  uint8_t* sm_red = sm_x + (size_t)(a.xrows + 1) * a.xpitch;  // + one all-zero activation row
+  const uint32_t sm_bar = smem_u32(sm_red + MT * SK_RED_BYTES_PER_MT);
   auto full_bar = [&](int s) { return sm_bar + 8u * (uint32_t)s; };
   auto empty_bar = [&](int s) { return sm_bar + 8u * (uint32_t)(stages + s); };
 
   const int grid = (int)gridDim.x;
-  const int m0 = (int)blockIdx.y * a.xrows;          // first activation row of this pass
-  const int mrows = min(a.xrows, a.M - m0);            // rows of this pass (the last may be short)
+  const int m0 = (int)blockIdx.y * a.xrows;  // first activation row of this pass
+  const int mrows = min(a.xrows, a.M - m0);   // rows of this pass (the last may be short)
   const int C = a.C;
-  const long long u0 = unit_begin(a.U, (int)blockIdx.x, grid);
-  const long long u1 = unit_begin(a.U, (int)blockIdx.x + 1, grid);
+  const Walk walk(unit_begin(a.U, (int)blockIdx.x, grid), unit_begin(a.U, (int)blockIdx.x + 1, grid), C);
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar(s), 33);  // lane 0's expect_tx arrive + one cp.async arrive per producer lane
-      mbar_init(empty_bar(s), SK_CONSUMERS);
+      mbar_init(empty_bar(s), SK_TILES);  // the four tile warps of the phase that consumes the stage
     }
     mbar_init_fence();
     tma_prefetch_desc(&tmap);
@@ -188,45 +240,68 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     // ------------------------------ producer ------------------------------
     constexpr int NGU = FMT == F_MX ? 8 : SK_KC / GS;  // scales per row per unit
     const int wG = words(a.G);
-    int s = 0;
-    uint32_t ph = 0;
-    int p = (int)(u0 / C), ch = (int)(u0 % C);
-    for (long long u = u0; u < u1; ++u) {
-      if (!mbar_wait(empty_bar(s), ph ^ 1u, a.status, ST_STREAM_EMPTY_TIMEOUT)) break;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(full_bar(s), SK_STAGE_Q);
-        tma_load_2d(sm_q + (uint32_t)s * SK_STAGE_Q, &tmap, ch * (SK_KC / 8), p * SK_ROWS, full_bar(s));
-      }
-      const uint32_t meta = sm_meta + (uint32_t)s * SK_META;
-#pragma unroll
-      for (int rr = 0; rr < SK_ROWS / 32; ++rr) {
-        const int r = lane + 32 * rr;
-        const int n = min(p * SK_ROWS + r, a.N - 1);  // rows past N: any valid row, never used
-        if (FMT == F_MX) {
-          cp_async<8>(meta + r * 16, (const uint8_t*)a.scales + (size_t)n * a.G + (size_t)ch * 8);
-        } else {
-          cp_async<NGU * 2>(meta + r * 16, (const __half*)a.scales + (size_t)n * a.G + (size_t)ch * NGU);
-          if (FMT == F_W4_ASYM)
-            cp_async<4>(meta + SK_META_SCALES + r * 4, a.zeros + (size_t)n * wG + (size_t)((ch * NGU) >> 3));
+    // Units are issued in bursts of SK_BURST consecutive units (adjacent 128-byte
+    // columns of the same rows): DRAM then sees 128*SK_BURST contiguous bytes per row at
+    // once instead of isolated 128-byte reads, which is what keeps its pages busy.
+    const int total = (int)(walk.u1 - walk.u0);
+    int sw = 0, si = 0;            // ring slot of the next unit to wait for / to issue
+    uint32_t phw = 0;              // parity of the wait cursor
+    int seg = 0, r = 0, len = 0, p = 0, ch = 0;
+    {
+      long long ua;
+      walk.segment(0, C, &ua, &len);
+      p = (int)(ua / C);
+      ch = (int)(ua - (long long)p * C);
+    }
+    for (int j0 = 0; j0 < total; j0 += SK_BURST) {
+      const int nb = min(SK_BURST, total - j0);
+      for (int b = 0; b < nb; ++b) {
+        if (!mbar_wait(empty_bar(sw), phw ^ 1u, a.status, ST_STREAM_EMPTY_TIMEOUT)) return;
+        if (++sw == stages) {
+          sw = 0;
+          phw ^= 1u;
         }
       }
-      cp_async_arrive_noinc(full_bar(s));
-      if (++s == stages) {
-        s = 0;
-        ph ^= 1u;
-      }
-      if (++ch == C) {
-        ch = 0;
-        ++p;
+      for (int b = 0; b < nb; ++b) {
+        const int s = si;
+        if (++si == stages) si = 0;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(full_bar(s), SK_STAGE_Q);
+          tma_load_2d(smem_u32(sm_q) + (uint32_t)s * SK_STAGE_Q, &tmap, ch * (SK_KC / 8), p * SK_ROWS, full_bar(s));
+        }
+        const uint32_t meta = smem_u32(sm_meta) + (uint32_t)s * SK_META;
+#pragma unroll
+        for (int rr = 0; rr < SK_ROWS / 32; ++rr) {
+          const int row = lane + 32 * rr;
+          const int n = min(p * SK_ROWS + row, a.N - 1);  // rows past N: any valid row, never used
+          if (FMT == F_MX) {
+            cp_async<8>(meta + row * 16, (const uint8_t*)a.scales + (size_t)n * a.G + (size_t)ch * 8);
+          } else {
+            cp_async<NGU * 2>(meta + row * 16, (const __half*)a.scales + (size_t)n * a.G + (size_t)ch * NGU);
+            if (FMT == F_W4_ASYM)
+              cp_async<4>(meta + SK_META_SCALES + row * 4, a.zeros + (size_t)n * wG + (size_t)((ch * NGU) >> 3));
+          }
+        }
+        cp_async_arrive_noinc(full_bar(s));
+        // advance the walk cursor
+        ++ch;
+        if (++r == len && seg + 1 < walk.nseg) {
+          long long ua;
+          walk.segment(++seg, C, &ua, &len);
+          p = (int)(ua / C);
+          ch = (int)(ua - (long long)p * C);
+          r = 0;
+        }
       }
     }
     return;
   }
 
   // -------------------------------- consumers --------------------------------
-  // Activations of this pass: rows m0 .. m0+xrows-1, FP16, each row re-ordered so
-  // that the 16 bytes a lane needs for word slot i of unit `ch` are
+  // Activations of this pass: rows m0 .. m0+mrows-1, FP16, each row re-ordered so
+  // that the 16 bytes a lane needs for word slot i of chunk `ch` are
   //   chunk (ch*32 + i*4 + c) = halves (h0,h4,h1,h5,h2,h6,h3,h7) of natural word (ch*32 + c*8 + i).
+  // Row `xrows` is all zero: lanes whose B-fragment column has no activation row read it.
   {
     const int cpr = a.K >> 3;  // 16-byte chunks per activation row
     const int total = mrows * cpr;
@@ -235,160 +310,226 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)(m0 + m) * a.K) + widx);
       const int ub = widx >> 5, wi = widx & 31;
       const int dst = (ub << 5) + ((wi & 7) << 2) + (wi >> 3);
-      sts128(sm_x + (uint32_t)m * (uint32_t)a.xpitch + ((uint32_t)dst << 4), pair_permute(v));
+      *reinterpret_cast<uint4*>(sm_x + (size_t)m * a.xpitch + ((size_t)dst << 4)) = pair_permute(v);
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * SK_CONSUMERS) : "memory");
+    for (int idx = tid; idx < cpr; idx += 32 * SK_CONSUMERS)
+      *reinterpret_cast<uint4*>(sm_x + (size_t)a.xrows * a.xpitch + ((size_t)idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
+    named_barrier(5, 32 * SK_CONSUMERS);
   }
 
+  const int tile = wid & (SK_TILES - 1), phase = wid >> 2;
   const int g = lane >> 2, c = lane & 3;
-  float acc[MT][4];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
-
-  const int p_first = (int)(u0 / C);
-  int p = p_first, ch = (int)(u0 % C), ch_begin = ch;
-  int s = 0;
-  uint32_t ph = 0;
-
-  // x rows this lane supplies as B-fragment column g (and g + 8 for the second m-tile)
+  // x rows this lane supplies as B-fragment column g (and g + 8 for the second m-tile).
+  // Lanes whose column has no activation row never load: their B registers stay zero.
   uint32_t xrow[MT];
   bool xok[MT];
+  uint4 xv[MT];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
     xok[mt] = (g + 8 * mt) < mrows;
-    xrow[mt] = sm_x + (uint32_t)(xok[mt] ? g + 8 * mt : 0) * (uint32_t)a.xpitch + ((uint32_t)c << 4);
+    xrow[mt] = smem_u32(sm_x) + (uint32_t)(xok[mt] ? g + 8 * mt : 0) * (uint32_t)a.xpitch + ((uint32_t)c << 4);
+    xv[mt] = make_uint4(0u, 0u, 0u, 0u);
   }
+  const size_t cta = (size_t)blockIdx.y * grid + blockIdx.x;
+  auto slot_ptr = [&](size_t which_cta, int slot) {
+    return reinterpret_cast<float4*>(a.ws) + (((which_cta * 2 + slot) * SK_TILES + tile) * MT) * 32;
+  };
+  const W4Consts kc = w4_consts();
+  const int ra = tile * 16 + g;  // row inside the box; ra & 7 == g
+  const uint32_t sw0 = ((uint32_t)(2 * c) ^ (uint32_t)g) << 4, sw1 = ((uint32_t)(2 * c + 1) ^ (uint32_t)g) << 4;
 
-  for (long long u = u0; u < u1; ++u) {
-    if (!mbar_wait(full_bar(s), ph, a.status, ST_STREAM_FULL_TIMEOUT)) return;
-    const int tile_row0 = p * SK_ROWS + wid * 16;
-    if (tile_row0 < a.N) {  // warp-uniform
-      const uint32_t qs = sm_q + (uint32_t)s * SK_STAGE_Q;
-      const uint32_t ra = (uint32_t)(wid * 16 + g);  // row inside the box; ra & 7 == g
-      const uint32_t offa = qs + ra * 128u, offb = offa + 8u * 128u;
-      const uint32_t c0 = ((uint32_t)(2 * c) ^ (uint32_t)g) << 4, c1 = ((uint32_t)(2 * c + 1) ^ (uint32_t)g) << 4;
-      const uint4 qa0 = lds128(offa + c0), qa1 = lds128(offa + c1);
-      const uint4 qb0 = lds128(offb + c0), qb1 = lds128(offb + c1);
-      const uint32_t meta = sm_meta + (uint32_t)s * SK_META;
-      Groups<FMT, GS> ga, gb;
-      ga.load(meta + ra * 16u, meta + SK_META_SCALES + ra * 4u, c, ch);
-      gb.load(meta + (ra + 8u) * 16u, meta + SK_META_SCALES + (ra + 8u) * 4u, c, ch);
-      const uint32_t xoff = (uint32_t)ch << 9;  // 32 chunks of 16 bytes per unit
+  // The CTA's units are numbered j = 0, 1, ... in walk order (the ring sequence);
+  // this warp handles j = phase, phase + 4, ... and tracks its ring slot incrementally.
+  int jbase = 0;       // j of the first unit of the current segment
+  int jw = phase;      // next j of this warp
+  int s = phase;       // ring slot of jw  (stages >= SK_PHASES)
+  uint32_t ph = 0;     // phase parity of that slot's full barrier
+  // A warp whose bounded wait ran out stops waiting and computing but keeps walking, so that
+  // the tile's named barriers are still met and the CTA ends instead of hanging.
+  bool alive = true;
+  for (int seg = 0; seg < walk.nseg; ++seg) {
+    long long ua;
+    int len;
+    walk.segment(seg, C, &ua, &len);
+    const int p = (int)(ua / C);
+    const int ch0 = (int)(ua - (long long)p * C);
+    const int tile_row0 = p * SK_ROWS + tile * 16;
+    const bool live = tile_row0 < a.N;  // warp-uniform
+
+    // Two accumulator sets per m-tile (even / odd MMA of a word pair): consecutive
+    // MMAs never wait on each other's result. They are added in a fixed order.
+    float acc[MT][2][4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        __half2 pa[4], pb[4];
-        ga.decode(word_of(qa0, qa1, i), i >> 2, pa);
-        gb.decode(word_of(qb0, qb1, i), i >> 2, pb);
-        if (HOOK && blockIdx.y == 0) {  // every pass decodes the same weights; one writes them
-          const int k = ch * SK_KC + 64 * c + 8 * i;
-          const int na = tile_row0 + g, nb = na + 8;
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (na < a.N) {
-              a.w_out[(size_t)na * a.K + k + j] = __low2half(pa[j]);
-              a.w_out[(size_t)na * a.K + k + j + 4] = __high2half(pa[j]);
-            }
-            if (nb < a.N) {
-              a.w_out[(size_t)nb * a.K + k + j] = __low2half(pb[j]);
-              a.w_out[(size_t)nb * a.K + k + j + 4] = __high2half(pb[j]);
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[mt][h][i] = 0.0f;
+
+    for (; jw < jbase + len; jw += SK_PHASES) {
+      const int r = jw - jbase;
+      const int s_now = s;
+      const uint32_t ph_now = ph;
+      s += SK_PHASES;
+      if (s >= stages) {
+        s -= stages;
+        ph ^= 1u;
+      }
+      if (alive && !mbar_wait(full_bar(s_now), ph_now, a.status, ST_STREAM_FULL_TIMEOUT)) alive = false;
+      if (!alive) continue;
+      if (live) {
+        const int ch = ch0 + r;
+        const uint8_t* qs = sm_q + (size_t)s_now * SK_STAGE_Q + (size_t)ra * 128;
+        const uint4 qa0 = *reinterpret_cast<const uint4*>(qs + sw0);
+        const uint4 qa1 = *reinterpret_cast<const uint4*>(qs + sw1);
+        const uint4 qb0 = *reinterpret_cast<const uint4*>(qs + 8 * 128 + sw0);
+        const uint4 qb1 = *reinterpret_cast<const uint4*>(qs + 8 * 128 + sw1);
+        const uint8_t* meta = sm_meta + (size_t)s_now * SK_META;
+        Groups<FMT, GS> ga, gb;
+        ga.load(meta + ra * 16, meta + SK_META_SCALES + ra * 4, c, ch);
+        gb.load(meta + (ra + 8) * 16, meta + SK_META_SCALES + (ra + 8) * 4, c, ch);
+        const uint32_t xoff = (uint32_t)ch << 9;  // 32 chunks of 16 bytes per unit
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          __half2 pa[4], pb[4];
+          ga.decode(word_of(qa0, qa1, i), i >> 2, kc, pa);
+          gb.decode(word_of(qb0, qb1, i), i >> 2, kc, pb);
+          if (HOOK && blockIdx.y == 0) {  // every pass decodes the same weights; one writes them
+            const int k = ch * SK_KC + 64 * c + 8 * i;
+            const int na = tile_row0 + g, nb = na + 8;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              if (na < a.N) {
+                a.w_out[(size_t)na * a.K + k + jj] = __low2half(pa[jj]);
+                a.w_out[(size_t)na * a.K + k + jj + 4] = __high2half(pa[jj]);
+              }
+              if (nb < a.N) {
+                a.w_out[(size_t)nb * a.K + k + jj] = __low2half(pb[jj]);
+                a.w_out[(size_t)nb * a.K + k + jj + 4] = __high2half(pb[jj]);
+              }
             }
           }
-        }
-        const uint32_t f0[4] = {h2_as_u32(pa[0]), h2_as_u32(pb[0]), h2_as_u32(pa[1]), h2_as_u32(pb[1])};
-        const uint32_t f1[4] = {h2_as_u32(pa[2]), h2_as_u32(pb[2]), h2_as_u32(pa[3]), h2_as_u32(pb[3])};
+          const uint32_t f0[4] = {h2_as_u32(pa[0]), h2_as_u32(pb[0]), h2_as_u32(pa[1]), h2_as_u32(pb[1])};
+          const uint32_t f1[4] = {h2_as_u32(pa[2]), h2_as_u32(pb[2]), h2_as_u32(pa[3]), h2_as_u32(pb[3])};
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
-          if (xok[mt]) xv = lds128(xrow[mt] + xoff + ((uint32_t)i << 6));
-          mma_16816(acc[mt], f0, xv.x, xv.y);
-          mma_16816(acc[mt], f1, xv.z, xv.w);
+          for (int mt = 0; mt < MT; ++mt) {
+            lds128_if(xv[mt], xrow[mt] + xoff + ((uint32_t)i << 6), xok[mt]);
+            mma_16816(acc[mt][0], f0, xv[mt].x, xv[mt].y);
+            mma_16816(acc[mt][1], f1, xv[mt].z, xv[mt].w);
+          }
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(s_now));
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty_bar(s));
-    if (++s == stages) {
-      s = 0;
-      ph ^= 1u;
+    jbase += len;
+
+    // ---- the CTA leaves panel p having covered chunks [ch0, ch0 + len) ----
+    float out[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) out[mt][i] = acc[mt][0][i] + acc[mt][1][i];
+    // the four phase warps of the tile: phases 1..3 hand their fragment to phase 0
+    float4* red = reinterpret_cast<float4*>(sm_red) + (size_t)(tile * (SK_PHASES - 1)) * MT * 32;
+    if (phase != 0) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+        red[((phase - 1) * MT + mt) * 32 + lane] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
     }
-    ++ch;
-    if (ch == C || u + 1 == u1) {
-      // ---- the CTA leaves panel p having covered chunks [ch_begin, ch) ----
-      if (tile_row0 < a.N) {
-        const bool whole = (ch_begin == 0 && ch == C);
-        float out[MT][4];
-        bool write = whole;
+    named_barrier(1 + tile, 32 * SK_PHASES);
+    if (phase == 0) {
+#pragma unroll
+      for (int f = 0; f < SK_PHASES - 1; ++f)  // fixed order: phase 1, 2, 3
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const float4 v = red[(f * MT + mt) * 32 + lane];
+          out[mt][0] += v.x;
+          out[mt][1] += v.y;
+          out[mt][2] += v.z;
+          out[mt][3] += v.w;
+        }
+    }
+    named_barrier(1 + tile, 32 * SK_PHASES);  // the exchange area may be reused
+    if (phase != 0 || !live || !alive) continue;
+
+    bool write = (ch0 == 0 && len == C);  // the whole K range was ours
+    if (!write) {
+      const int b_first = unit_owner(a.U, (long long)p * C, grid);
+      const int b_last = unit_owner(a.U, (long long)(p + 1) * C - 1, grid);
+      int* cnt = a.counters + ((size_t)blockIdx.y * a.P + p) * SK_TILES + tile;
+      if ((int)blockIdx.x != b_last) {
+        // park the fragment; the owner of the panel's end collects it
+        const int slot = ((int)(walk.u0 / C) == p) ? 0 : 1;
+        float4* mine = slot_ptr(cta, slot);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          mine[mt * 32 + lane] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();  // the warp's parked fragment is visible before the counter moves
+          atomicAdd(cnt, 1);
+        }
+      } else {
+        // owner: wait (bounded) until the b_last - b_first others have parked, add in CTA order
+        int ok = 1;
+        if (lane == 0) {
+          const long long t0 = clock64();
+          while (*reinterpret_cast<volatile int*>(cnt) < b_last - b_first) {
+            __nanosleep(64);
+            if (clock64() - t0 > kWaitLimitCycles) {
+              atomicExch(a.status, ST_STREAM_PANEL_TIMEOUT);
+              ok = 0;
+              break;
+            }
+          }
+          __threadfence();
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          alive = false;
+          continue;
+        }
+        float sum[MT][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) out[mt][i] = acc[mt][i];
-        if (!whole) {
-          const int slot = (p == p_first) ? 0 : 1;
-          const size_t cta = (size_t)blockIdx.y * grid + blockIdx.x;
-          float4* mine = reinterpret_cast<float4*>(a.ws) + (((cta * 2 + slot) * SK_CONSUMERS + wid) * MT) * 32;
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-            mine[mt * 32 + lane] = make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
-          __threadfence();
-          __syncwarp();
-          const int b_first = unit_owner(a.U, (long long)p * C, grid);
-          const int b_last = unit_owner(a.U, (long long)(p + 1) * C - 1, grid);
-          int* cnt = a.counters + ((size_t)blockIdx.y * a.P + p) * SK_CONSUMERS + wid;
-          int old = 0;
-          if (lane == 0) old = atomicAdd(cnt, 1);
-          old = __shfl_sync(0xffffffffu, old, 0);
-          if (old == b_last - b_first) {  // last of (b_last - b_first + 1) contributors
-            __threadfence();
-            write = true;
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-              for (int i = 0; i < 4; ++i) out[mt][i] = 0.0f;
-            for (int b = b_first; b <= b_last; ++b) {  // fixed order: by CTA, not by arrival
-              const int sl = ((int)(unit_begin(a.U, b, grid) / C) == p) ? 0 : 1;
-              const size_t ob = (size_t)blockIdx.y * grid + b;
-              const float4* theirs =
-                  reinterpret_cast<const float4*>(a.ws) + (((ob * 2 + sl) * SK_CONSUMERS + wid) * MT) * 32;
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) {
-                const float4 v = __ldcg(theirs + mt * 32 + lane);
-                out[mt][0] += v.x;
-                out[mt][1] += v.y;
-                out[mt][2] += v.z;
-                out[mt][3] += v.w;
-              }
-            }
-            if (lane == 0) *cnt = 0;  // ready for the next launch
-          }
-        }
-        if (write) {
-          const int na = tile_row0 + g, nb = na + 8;
+          for (int i = 0; i < 4; ++i) sum[mt][i] = 0.0f;
+        for (int b = b_first; b < b_last; ++b) {  // fixed order: by CTA, never by arrival
+          const int their_slot = ((int)(unit_begin(a.U, b, grid) / C) == p) ? 0 : 1;
+          const float4* theirs = slot_ptr((size_t)blockIdx.y * grid + b, their_slot);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            const int col = 8 * mt + 2 * c;  // activation row within this pass
-            const int m = m0 + col;
-            if (col < mrows) {
-              if (na < a.N) a.c[(size_t)m * a.N + na] = __float2half_rn(out[mt][0]);
-              if (nb < a.N) a.c[(size_t)m * a.N + nb] = __float2half_rn(out[mt][2]);
-            }
-            if (col + 1 < mrows) {
-              if (na < a.N) a.c[(size_t)(m + 1) * a.N + na] = __float2half_rn(out[mt][1]);
-              if (nb < a.N) a.c[(size_t)(m + 1) * a.N + nb] = __float2half_rn(out[mt][3]);
-            }
+            const float4 v = __ldcg(theirs + mt * 32 + lane);
+            sum[mt][0] += v.x;
+            sum[mt][1] += v.y;
+            sum[mt][2] += v.z;
+            sum[mt][3] += v.w;
           }
         }
-      }
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+        for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.0f;
-      if (ch == C) {
-        ch = 0;
-        ++p;
+          for (int i = 0; i < 4; ++i) out[mt][i] = sum[mt][i] + out[mt][i];
+        if (lane == 0) *cnt = 0;  // ready for the next launch
+        write = true;
       }
-      ch_begin = ch;
+    }
+    if (write) {
+      const int na = tile_row0 + g, nb = na + 8;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const int col = 8 * mt + 2 * c;  // activation row within this pass
+        const int m = m0 + col;
+        if (col < mrows) {
+          if (na < a.N) a.c[(size_t)m * a.N + na] = __float2half_rn(out[mt][0]);
+          if (nb < a.N) a.c[(size_t)m * a.N + nb] = __float2half_rn(out[mt][2]);
+        }
+        if (col + 1 < mrows) {
+          if (na < a.N) a.c[(size_t)(m + 1) * a.N + na] = __float2half_rn(out[mt][1]);
+          if (nb < a.N) a.c[(size_t)(m + 1) * a.N + nb] = __float2half_rn(out[mt][3]);
+        }
+      }
     }
   }
 }
@@ -437,11 +578,13 @@ cudaError_t launch_fmt(const CUtensorMap& tmap, const StreamParams& sp, int mt, 
               : launch_one<FMT, GS, 2, false>(tmap, sp, grid, smem, stream);
 }
 
-}  // namespace
+constexpr int kSmemBudget = 232448 - 1024 /* alignment slack */ - SK_BAR_BYTES;
+// ring depth that fits beside `rows` activation rows (+ the zero row) and the exchange area
+int stages_for(int rows, int K) {
+  const int mt = rows > 8 ? 2 : 1;
+  return (kSmemBudget - (rows + 1) * (K * 2 + 64) - mt * SK_RED_BYTES_PER_MT) / (SK_STAGE_Q + SK_META);
+}
 
-namespace {
-constexpr int kSmemBudget = 232448 - 1024 /* alignment slack */ - 2 * 8 * SK_MAX_STAGES /* barriers */;
-int stages_for(int rows, int K) { return (kSmemBudget - rows * (K * 2 + 64)) / (SK_STAGE_Q + SK_META); }
 }  // namespace
 
 bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, const void* scales,
@@ -450,16 +593,16 @@ bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, cons
   if (gs_or_0_for_mx != 0 && gs_or_0_for_mx != 32 && gs_or_0_for_mx != 64 && gs_or_0_for_mx != 128)
     return false;
   if (((uintptr_t)q | (uintptr_t)scales | (uintptr_t)x) & 15u) return false;
-  if (K > 65536 || stages_for(1, K) < 4) return false;  // one activation row must fit beside a 4-stage ring
+  if (K > 65536 || stages_for(1, K) < 8) return false;  // one activation row must fit beside an 8-stage ring
   return encode_tiled() != nullptr;
 }
 
 void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan) {
   const int xpitch = K * 2 + 64;
-  // activation rows per pass: 16 if they leave room for a 4-stage ring, else 8, else fewer
+  // activation rows per pass: 16 if they leave room for an 8-stage ring, else 8, else fewer
   int rows = M < 16 ? M : 16;
-  if (rows > 8 && stages_for(rows, K) < 4) rows = 8;
-  while (rows > 1 && stages_for(rows, K) < 4) --rows;
+  if (rows > 8 && stages_for(rows, K) < 8) rows = 8;
+  while (rows > 1 && stages_for(rows, K) < 8) --rows;
   plan->rows_per_pass = rows;
   plan->mt = rows > 8 ? 2 : 1;
   plan->passes = (M + rows - 1) / rows;
@@ -470,9 +613,10 @@ void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan) {
   plan->U = (long long)plan->P * plan->C;
   plan->grid_x = (int)(plan->U < sm_count ? plan->U : sm_count);
   plan->xpitch = xpitch;
-  plan->smem = 1024 + (size_t)plan->stages * (SK_STAGE_Q + SK_META) + (size_t)rows * xpitch + 2 * 8 * SK_MAX_STAGES;
-  plan->ws_bytes = (size_t)plan->passes * plan->grid_x * 2 * SK_CONSUMERS * plan->mt * 32 * sizeof(float4);
-  plan->counter_ints = (size_t)plan->passes * plan->P * SK_CONSUMERS;
+  plan->smem = 1024 + (size_t)plan->stages * (SK_STAGE_Q + SK_META) + (size_t)(rows + 1) * xpitch +
+               (size_t)plan->mt * SK_RED_BYTES_PER_MT + SK_BAR_BYTES;
+  plan->ws_bytes = (size_t)plan->passes * plan->grid_x * 2 * SK_TILES * plan->mt * 32 * sizeof(float4);
+  plan->counter_ints = (size_t)plan->passes * plan->P * SK_TILES;
 }
 
 // Launches the stream GEMM. `fmt`: 0 = W4 symmetric, 1 = W4 asymmetric, 2 = MXFP4.
@@ -511,7 +655,6 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   sp.ws = ws;
   sp.counters = counters;
   sp.status = status;
-
   sp.xrows = plan.rows_per_pass;
   const dim3 grid((unsigned)plan.grid_x, (unsigned)plan.passes);  // pass y = activation rows y*rows_per_pass ...
   switch (fmt) {

@@ -21,6 +21,7 @@ enum : int {
   ST_OK = 0,
   ST_STREAM_FULL_TIMEOUT = 101,   // stream GEMM: a consumer never saw its stage filled
   ST_STREAM_EMPTY_TIMEOUT = 102,  // stream GEMM: the producer never got a stage back
+  ST_STREAM_PANEL_TIMEOUT = 103,  // stream GEMM: a panel owner never saw the other CTAs' fragments
   ST_TENSOR_TIMEOUT = 201,        // tensor GEMM: a pipeline wait ran out
   ST_FLASH_TIMEOUT = 301,         // flash decode: a pipeline wait ran out
 };
@@ -90,22 +91,58 @@ __device__ __forceinline__ W4Group w4_group(__half s, uint32_t z) {
   return g;
 }
 
+// (a & b) | c in one LOP3 (the constants are kept in registers by the assembler).
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 // (code | 0x6400) is the half 1024 + code; (code<<4 | 0x6400) is 1024 + 16*code.
 // Subtracting 1024 + z (or fma by 1/16 and adding -(64+z)) gives the integer
 // code - z exactly; the half multiply by s then rounds the exact product once,
 // which is what dq_w4_scalar does in float. Subnormal results are kept.
-__device__ __forceinline__ void dq_w4_word(uint32_t qw, const W4Group& g, __half2 out[4]) {
-  const uint32_t kMagic = 0x64006400u;
-  const __half2 k16th = u32_as_h2(0x2C002C00u);  // (1/16, 1/16)
+// 13 instructions per word: 1 shift, 4 LOP3, 2 HADD2, 2 HFMA2, 4 HMUL2.
+//
+// The four constants come from `mov` instructions the compiler cannot see
+// through: it then keeps them in registers for the whole kernel instead of
+// re-creating them next to every use (which costs an instruction per use).
+struct W4Consts {
+  uint32_t magic, lo, hi;
+  __half2 sixteenth;
+};
+
+__device__ __forceinline__ W4Consts w4_consts() {
+  W4Consts k;
+  uint32_t s;
+  asm volatile("mov.b32 %0, 0x64006400;" : "=r"(k.magic));
+  asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(k.lo));
+  asm volatile("mov.b32 %0, 0x00F000F0;" : "=r"(k.hi));
+  asm volatile("mov.b32 %0, 0x2C002C00;" : "=r"(s));  // (1/16, 1/16)
+  k.sixteenth = u32_as_h2(s);
+  return k;
+}
+
+__device__ __forceinline__ void dq_w4_word(uint32_t qw, const W4Group& g, const W4Consts& k, __half2 out[4]) {
   const uint32_t hi = qw >> 8;
-  const __half2 t0 = u32_as_h2((qw & 0x000F000Fu) | kMagic);
-  const __half2 t1 = u32_as_h2((qw & 0x00F000F0u) | kMagic);
-  const __half2 t2 = u32_as_h2((hi & 0x000F000Fu) | kMagic);
-  const __half2 t3 = u32_as_h2((hi & 0x00F000F0u) | kMagic);
+  const __half2 t0 = u32_as_h2(and_or(qw, k.lo, k.magic));
+  const __half2 t1 = u32_as_h2(and_or(qw, k.hi, k.magic));
+  const __half2 t2 = u32_as_h2(and_or(hi, k.lo, k.magic));
+  const __half2 t3 = u32_as_h2(and_or(hi, k.hi, k.magic));
   out[0] = __hmul2_rn(__hsub2_rn(t0, g.za), g.s2);
-  out[1] = __hmul2_rn(__hfma2(t1, k16th, g.zb), g.s2);
+  out[1] = __hmul2_rn(__hfma2(t1, k.sixteenth, g.zb), g.s2);
   out[2] = __hmul2_rn(__hsub2_rn(t2, g.za), g.s2);
-  out[3] = __hmul2_rn(__hfma2(t3, k16th, g.zb), g.s2);
+  out[3] = __hmul2_rn(__hfma2(t3, k.sixteenth, g.zb), g.s2);
+}
+
+// Convenience form for code that decodes a handful of words.
+__device__ __forceinline__ void dq_w4_word(uint32_t qw, const W4Group& g, __half2 out[4]) {
+  W4Consts k;
+  k.magic = 0x64006400u;
+  k.lo = 0x000F000Fu;
+  k.hi = 0x00F000F0u;
+  k.sixteenth = u32_as_h2(0x2C002C00u);
+  dq_w4_word(qw, g, k, out);
 }
 
 // MXFP4 block multiplier. An E2M1 code placed as sign -> bit 15 and (e1 e0 m)
@@ -132,10 +169,10 @@ __device__ __forceinline__ MxBlock mx_block(uint32_t se) {
 __device__ __forceinline__ void dq_mx_word(uint32_t qw, const MxBlock& b, __half2 out[4]) {
   if (b.fast) {
     const uint32_t kMag = 0x0E000E00u, kSign = 0x80008000u;
-    const uint32_t r0 = ((qw << 9) & kMag) | ((qw << 12) & kSign);
-    const uint32_t r1 = ((qw << 5) & kMag) | ((qw << 8) & kSign);
-    const uint32_t r2 = ((qw << 1) & kMag) | ((qw << 4) & kSign);
-    const uint32_t r3 = ((qw >> 3) & kMag) | (qw & kSign);
+    const uint32_t r0 = and_or(qw << 12, kSign, (qw << 9) & kMag);
+    const uint32_t r1 = and_or(qw << 8, kSign, (qw << 5) & kMag);
+    const uint32_t r2 = and_or(qw << 4, kSign, (qw << 1) & kMag);
+    const uint32_t r3 = and_or(qw, kSign, (qw >> 3) & kMag);
     out[0] = __hmul2_rn(u32_as_h2(r0), b.h2);
     out[1] = __hmul2_rn(u32_as_h2(r1), b.h2);
     out[2] = __hmul2_rn(u32_as_h2(r2), b.h2);
@@ -175,16 +212,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                : "memory");
 }
 
+// One try_wait: the hardware parks the thread until the phase completes or about
+// `kSuspendNs` have passed, whichever is first, so a waiting warp issues almost nothing.
+constexpr uint32_t kSuspendNs = 20000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendNs)
       : "memory");
   return ok != 0;
 }
@@ -248,7 +289,7 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 // D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
 __device__ __forceinline__ void mma_16816(float d[4], const uint32_t a[4], uint32_t b0,
                                           uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -261,6 +302,20 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "r"(addr));
   return v;
+}
+
+// 16-byte shared load executed only where `on` is set; elsewhere v keeps its value
+// and the lane generates no shared-memory traffic.
+__device__ __forceinline__ void lds128_if(uint4& v, uint32_t addr, bool on) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.u32 p, %5, 0;\n"
+      "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+      "}\n"
+      : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+      : "r"(addr), "r"((uint32_t)on)
+      : "memory");
 }
 
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
