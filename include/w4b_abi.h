@@ -125,6 +125,18 @@ int w4b_gemm_mx(const w4b_packed_mx* p, const void* x, void* c, int M, int path,
 int w4b_gemm_w4_hostio(const w4b_packed_w4* p, const void* x_host, void* c_host, int M, int path,
                        void* stream);
 
+/* The stream GEMM without any allocation. It has no counterpart in the reference.
+ * For callers that cannot call cudaMalloc (a stream being captured into a graph,
+ * a process whose memory pool owns the device, a no-allocation serving loop): the
+ * kernel's scratch lives in a fixed 3.25 MiB array inside the library image, held by
+ * every device that loads the library. Serves only shapes of the stream kernel
+ * (K % 256 == 0, N >= 64, gs 32/64/128, 16-byte aligned q / scales / x) whose scratch
+ * fits (M <= 16 with N <= 1,000,000 always does); anything else returns W4B_INVALID.
+ * The first call on a device resolves the
+ * array's address and clears it: make it before any stream capture. All calls share
+ * the array; calls that overlap on the GPU race on it. */
+int w4b_gemm_w4_noalloc(const w4b_packed_w4* p, const void* x, void* c, int M, void* stream);
+
 /* ---- stand-alone dequantisation (two-pass comparator, bitwise gate) ---- */
 
 /* dequant (include/w4/dequant.cuh:62-82): w is N*K FP16. */

@@ -60,6 +60,7 @@ ABI = {
     "w4b_gemm_w4": (_I, [C.POINTER(_PackedW4), _P, _P, _I, _I, _P, _P]),
     "w4b_gemm_mx": (_I, [C.POINTER(_PackedMx), _P, _P, _I, _I, _P, _P]),
     "w4b_gemm_w4_hostio": (_I, [C.POINTER(_PackedW4), _P, _P, _I, _I, _P]),
+    "w4b_gemm_w4_noalloc": (_I, [C.POINTER(_PackedW4), _P, _P, _I, _P]),
     "w4b_dequant_w4": (_I, [C.POINTER(_PackedW4), _P, _P]),
     "w4b_dequant_mx": (_I, [C.POINTER(_PackedMx), _P, _P]),
     "w4b_dequant_f8": (_I, [_P, _P, _P, _I, _I, _I, _P]),
@@ -194,6 +195,12 @@ def gemm_mma_mx(p, x, c, M, stream=None, w_out=None):  # mxfused.cuh:291
 def gemm_hostio(p: DevicePackedW, x_host, c_host, M, stream=None, path=PATH_AUTO):
     """x_host / c_host are HOST addresses (pinned for full speed); weights stay on the device."""
     _check(lib.w4b_gemm_w4_hostio(C.byref(p._c()), x_host, c_host, M, path, stream))
+
+
+def gemm_noalloc(p: DevicePackedW, x, c, M, stream=None):
+    """The stream GEMM with its scratch in a fixed array of the library image: for callers
+    that may not allocate (graph capture, pooled memory, no-allocation serving loops)."""
+    _check(lib.w4b_gemm_w4_noalloc(C.byref(p._c()), x, c, M, stream))
 
 
 def gemm_route(p, M, path=PATH_AUTO, x=16) -> int:

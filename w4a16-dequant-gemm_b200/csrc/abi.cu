@@ -181,6 +181,10 @@ int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint3
 
 }  // namespace
 
+namespace w4b {
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+}  // namespace w4b
+
 extern "C" {
 
 const char* w4b_last_error(void) { return g_err; }

@@ -12,6 +12,10 @@ namespace w4b {
 // 32-bit words that hold n 4-bit codes (the reference's words(), include/w4/pack.hpp:33).
 __host__ __device__ __forceinline__ int words(int n) { return (n + 7) >> 3; }
 
+// ---- abi.cu ------------------------------------------------------------------
+// Sets the calling thread's message returned by w4b_last_error().
+void set_last_error(const char* msg);
+
 // ---- dequant.cu -----------------------------------------------------------
 cudaError_t dequant_w4_launch(const uint32_t* q, const __half* scales, const uint32_t* zeros, int N, int K,
                               int gs, int G, int symmetric, __half* w, cudaStream_t stream);
