@@ -4,3 +4,4 @@ capi.py binds the ABI and mirrors the reference's entry points."""
 from . import build  # noqa: F401
 from .capi import *  # noqa: F401,F403
 from . import capi  # noqa: F401
+from . import shard  # noqa: F401
