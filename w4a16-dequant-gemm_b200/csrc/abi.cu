@@ -146,20 +146,29 @@ int check_gemm_bounds(int N, int M, int entry, const char* who) {
   return W4B_OK;
 }
 
-// Chooses the kernel: the requested one when the shape fits it, else generic.
-// (The tensor kernel is served by the stream kernel's shape rules until it has
-// its own; both fall back to the generic kernel.)
-int route_kernel(int entry, int N, int K, int gs_or_0, const void* q, const void* scales, const void* x) {
+// Chooses the kernel: the requested one when the shape fits it, else the other fast
+// kernel, else generic. `w_out` matters because the tensor kernel's hook stores 16 bytes.
+int route_kernel(int entry, int N, int K, int gs_or_0, const void* q, const void* scales, const void* x,
+                 const void* w_out = nullptr) {
   if (entry == W4B_PATH_GENERIC) return W4B_PATH_GENERIC;
-  if (stream_gemm_supported(N, K, gs_or_0, q, scales, x)) return W4B_PATH_STREAM;
-  return W4B_PATH_GENERIC;
+  const bool tensor_ok = tensor_gemm_supported(N, K, q, x) && (((uintptr_t)w_out & 15u) == 0);
+  const bool stream_ok = stream_gemm_supported(N, K, gs_or_0, q, scales, x);
+  if (entry == W4B_PATH_TENSOR) return tensor_ok ? W4B_PATH_TENSOR : (stream_ok ? W4B_PATH_STREAM : W4B_PATH_GENERIC);
+  return stream_ok ? W4B_PATH_STREAM : W4B_PATH_GENERIC;
 }
 
 int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros, int N, int K, int G,
              const void* x, void* c, int M, int entry, cudaStream_t stream, void* w_out, const char* who) {
   DeviceCtx* ctx = nullptr;
   if (int rc = get_ctx(&ctx)) return rc;
-  const int kernel = route_kernel(entry, N, K, fmt == 2 ? 0 : gs, q, scales, x);
+  const int kernel = route_kernel(entry, N, K, fmt == 2 ? 0 : gs, q, scales, x, w_out);
+  if (kernel == W4B_PATH_TENSOR) {
+    CUDA_TRY(tensor_gemm_launch(fmt, gs, q, scales, zeros, N, K, G, (const __half*)x, (__half*)c, M, (__half*)w_out,
+                                ctx->status, stream),
+             who);
+    g_launches += 1;
+    return W4B_OK;
+  }
   if (kernel == W4B_PATH_STREAM) {
     StreamPlan plan;
     stream_gemm_plan(N, K, M, ctx->sm_count, &plan);

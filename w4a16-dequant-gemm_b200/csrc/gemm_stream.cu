@@ -75,7 +75,7 @@ struct StreamParams {
   int N, K, M;
   int G;        // scales per row: groups (W4) or 32-blocks (MX)
   int C, P;     // 256-k chunks per row, 64-row panels
-  long long U;  // units = P * C
+  int U;        // units = P * C  (U * grid < 2^31: all unit arithmetic is 32-bit)
   int stages;
   int xrows;    // activation rows per pass (<= 8*MT); pass y covers rows y*xrows ...
   int xpitch;   // bytes between activation rows in shared memory (== 64 mod 128)
@@ -84,12 +84,14 @@ struct StreamParams {
   int* status;
 };
 
-__host__ __device__ __forceinline__ long long unit_begin(long long U, int b, int grid) {
-  return U * (long long)b / grid;
+// Unit arithmetic is unsigned 32-bit (the launcher guarantees U * grid < 2^31): 64-bit
+// divisions would cost every warp microseconds per launch.
+__host__ __device__ __forceinline__ int unit_begin(int U, int b, int grid) {
+  return (int)((unsigned)U * (unsigned)b / (unsigned)grid);
 }
 // The CTA whose range holds unit t (ranges are [U*b/grid, U*(b+1)/grid)).
-__device__ __forceinline__ int unit_owner(long long U, long long t, int grid) {
-  return (int)(((t + 1) * grid + U - 1) / U) - 1;
+__device__ __forceinline__ int unit_owner(int U, int t, int grid) {
+  return (int)((((unsigned)t + 1u) * (unsigned)grid + (unsigned)U - 1u) / (unsigned)U) - 1;
 }
 
 // The order in which a CTA walks its range [u0, u1): the part of the last panel
@@ -97,26 +99,26 @@ __device__ __forceinline__ int unit_owner(long long U, long long t, int grid) {
 // the first panel (whose end this CTA owns). A range inside one panel is one
 // segment.
 struct Walk {
-  long long u0, u1, pb, pe;
+  int u0, u1, pb, pe;
   int len_tail, n_full, len_head, nseg;
   bool single;
-  __device__ Walk(long long a, long long b, int C) : u0(a), u1(b) {
+  __device__ Walk(int a, int b, int C) : u0(a), u1(b) {
     pb = (u0 + C - 1) / C * C;  // first panel boundary at or after u0
     pe = u1 / C * C;            // last panel boundary at or before u1
     single = pb > pe;           // no boundary inside [u0, u1]: the range lies within one panel
     if (single) {
       len_tail = n_full = 0;
-      len_head = (int)(u1 - u0);
+      len_head = u1 - u0;
       nseg = 1;
     } else {
-      len_tail = (int)(u1 - pe);
-      n_full = (int)((pe - pb) / C);
-      len_head = (int)(pb - u0);
+      len_tail = u1 - pe;
+      n_full = (pe - pb) / C;
+      len_head = pb - u0;
       nseg = (len_tail > 0) + n_full + (len_head > 0);
     }
   }
   // segment i -> first unit and length (all units of a segment lie in one panel)
-  __device__ void segment(int i, int C, long long* ua, int* len) const {
+  __device__ void segment(int i, int C, int* ua, int* len) const {
     if (single) {
       *ua = u0;
       *len = len_head;
@@ -131,7 +133,7 @@ struct Walk {
       --i;
     }
     if (i < n_full) {
-      *ua = pb + (long long)i * C;
+      *ua = pb + i * C;
       *len = C;
       return;
     }
@@ -226,14 +228,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
   const int C = a.C;
   const Walk walk(unit_begin(a.U, (int)blockIdx.x, grid), unit_begin(a.U, (int)blockIdx.x + 1, grid), C);
 
-  if (tid == 0) {
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(full_bar(s), 33);  // lane 0's expect_tx arrive + one cp.async arrive per producer lane
-      mbar_init(empty_bar(s), SK_TILES);  // the four tile warps of the phase that consumes the stage
-    }
+  if (tid < stages) {
+    mbar_init(full_bar(tid), 33);  // lane 0's expect_tx arrive + one cp.async arrive per producer lane
+    mbar_init(empty_bar(tid), SK_TILES);  // the four tile warps of the phase that consumes the stage
     mbar_init_fence();
-    tma_prefetch_desc(&tmap);
   }
+  if (tid == 32 * SK_CONSUMERS) tma_prefetch_desc(&tmap);
   __syncthreads();
 
   if (wid == SK_CONSUMERS) {
@@ -243,15 +243,15 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     // Units are issued in bursts of SK_BURST consecutive units (adjacent 128-byte
     // columns of the same rows): DRAM then sees 128*SK_BURST contiguous bytes per row at
     // once instead of isolated 128-byte reads, which is what keeps its pages busy.
-    const int total = (int)(walk.u1 - walk.u0);
+    const int total = walk.u1 - walk.u0;
     int sw = 0, si = 0;            // ring slot of the next unit to wait for / to issue
     uint32_t phw = 0;              // parity of the wait cursor
     int seg = 0, r = 0, len = 0, p = 0, ch = 0;
     {
-      long long ua;
+      int ua;
       walk.segment(0, C, &ua, &len);
-      p = (int)(ua / C);
-      ch = (int)(ua - (long long)p * C);
+      p = ua / C;
+      ch = ua - p * C;
     }
     for (int j0 = 0; j0 < total; j0 += SK_BURST) {
       const int nb = min(SK_BURST, total - j0);
@@ -286,10 +286,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
         // advance the walk cursor
         ++ch;
         if (++r == len && seg + 1 < walk.nseg) {
-          long long ua;
+          int ua;
           walk.segment(++seg, C, &ua, &len);
-          p = (int)(ua / C);
-          ch = (int)(ua - (long long)p * C);
+          p = ua / C;
+          ch = ua - p * C;
           r = 0;
         }
       }
@@ -348,11 +348,10 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
   // the tile's named barriers are still met and the CTA ends instead of hanging.
   bool alive = true;
   for (int seg = 0; seg < walk.nseg; ++seg) {
-    long long ua;
-    int len;
+    int ua, len;
     walk.segment(seg, C, &ua, &len);
-    const int p = (int)(ua / C);
-    const int ch0 = (int)(ua - (long long)p * C);
+    const int p = ua / C;
+    const int ch0 = ua - p * C;
     const int tile_row0 = p * SK_ROWS + tile * 16;
     const bool live = tile_row0 < a.N;  // warp-uniform
 
@@ -455,12 +454,12 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
 
     bool write = (ch0 == 0 && len == C);  // the whole K range was ours
     if (!write) {
-      const int b_first = unit_owner(a.U, (long long)p * C, grid);
-      const int b_last = unit_owner(a.U, (long long)(p + 1) * C - 1, grid);
+      const int b_first = unit_owner(a.U, p * C, grid);
+      const int b_last = unit_owner(a.U, (p + 1) * C - 1, grid);
       int* cnt = a.counters + ((size_t)blockIdx.y * a.P + p) * SK_TILES + tile;
       if ((int)blockIdx.x != b_last) {
         // park the fragment; the owner of the panel's end collects it
-        const int slot = ((int)(walk.u0 / C) == p) ? 0 : 1;
+        const int slot = (walk.u0 / C == p) ? 0 : 1;
         float4* mine = slot_ptr(cta, slot);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -496,7 +495,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
 #pragma unroll
           for (int i = 0; i < 4; ++i) sum[mt][i] = 0.0f;
         for (int b = b_first; b < b_last; ++b) {  // fixed order: by CTA, never by arrival
-          const int their_slot = ((int)(unit_begin(a.U, b, grid) / C) == p) ? 0 : 1;
+          const int their_slot = (unit_begin(a.U, b, grid) / C == p) ? 0 : 1;
           const float4* theirs = slot_ptr((size_t)blockIdx.y * grid + b, their_slot);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
@@ -594,6 +593,8 @@ bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, cons
     return false;
   if (((uintptr_t)q | (uintptr_t)scales | (uintptr_t)x) & 15u) return false;
   if (K > 65536 || stages_for(1, K) < 8) return false;  // one activation row must fit beside an 8-stage ring
+  // 32-bit unit arithmetic: units * CTAs below 2^31 (>= 100 GB of packed weights on 148 SMs)
+  if ((long long)((N + SK_ROWS - 1) / SK_ROWS) * (K / SK_KC) * 1024 >= (1LL << 31)) return false;
   return encode_tiled() != nullptr;
 }
 
@@ -649,7 +650,7 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   sp.G = G;
   sp.C = plan.C;
   sp.P = plan.P;
-  sp.U = plan.U;
+  sp.U = (int)plan.U;
   sp.stages = plan.stages;
   sp.xpitch = plan.xpitch;
   sp.ws = ws;

@@ -52,6 +52,12 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
                                const StreamPlan& plan, float* ws, int* counters, int* status,
                                cudaStream_t stream);
 
+// ---- gemm_tensor.cu ---------------------------------------------------------
+bool tensor_gemm_supported(int N, int K, const void* q, const void* x);
+cudaError_t tensor_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros, int N,
+                               int K, int G, const __half* x, __half* c, int M, __half* w_out, int* status,
+                               cudaStream_t stream);
+
 // ---- attn_flash.cu ----------------------------------------------------------
 enum : int { ATTN_FP16 = 0, ATTN_W4_SYM = 1, ATTN_W4_ASYM = 2, ATTN_F8 = 3 };
 // Where the K / V rows of one call live. Head h owns rows [h*slab_rows, (h+1)*slab_rows)
