@@ -191,33 +191,23 @@ def run_mine(args):
             step(i)
         torch.cuda.synchronize()
 
-    # The K steps are captured once in a CUDA graph (the GEMM launches and, on several GPUs, the
-    # NCCL all-gathers) so that the timed region holds device work only.
+    # On one GPU the K steps are captured once in a CUDA graph, so the timed region holds device work
+    # only. With NCCL in the step the steps are launched eagerly: capturing the collectives hung here
+    # (both ranks stalled after capture), so that route is not taken.
     launches_before = w4.launch_count()
-    use_graph = True
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    try:
-        with torch.cuda.graph(graph, stream=side):
-            sstream = torch.cuda.current_stream().cuda_stream
+    use_graph = world == 1
+    if use_graph:
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            sstream = side.cuda_stream
+            graph.capture_begin()
             for i in range(args.steps):
                 w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, sstream)
-                if world > 1:
-                    dist.all_gather_into_tensor(gathered.view(-1), c.view(-1))
+            graph.capture_end()
         launches_captured = w4.launch_count() - launches_before
         graph.replay()  # untimed: uploads the graph
         torch.cuda.synchronize()
-    except Exception as e:  # capture of the collective refused: time eager steps instead
-        if world == 1:
-            raise
-        use_graph = False
-        print(f"[bench] graph capture failed on rank {rank}: {e}", file=sys.stderr)
-        torch.cuda.synchronize()
-    if world > 1:  # all ranks must take the same route
-        flag = torch.tensor([1 if use_graph else 0], device=device)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        use_graph = bool(flag.item())
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
@@ -296,8 +286,7 @@ def run_mine(args):
         "config": {"workload": WORKLOAD, "us_per_gemm": round(us_per_step, 3),
                    "algorithmic_bytes_per_gemm": bytes_per_gemm,
                    "l2": f"weights rotate over {copies} copies ({copies * bytes_per_gemm / 1e6:.0f} MB > 126 MB L2)",
-                   "timing": ("one CUDA graph of K steps (GEMM" + (" + NCCL all-gather" if world > 1 else "") +
-                              "), CUDA events" + (", max over ranks" if world > 1 else "")) if use_graph else
+                   "timing": "one CUDA graph of K launches, CUDA events" if use_graph else
                              "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks",
                    "parallelism": "single GPU" if world == 1 else f"column-parallel N x{world} + all-gather",
                    "rel_l2_vs_fp32_product": rel},
