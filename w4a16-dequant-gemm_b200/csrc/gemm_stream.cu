@@ -60,8 +60,9 @@ constexpr int SK_CONSUMERS = SK_TILES * SK_PHASES;
 constexpr int SK_THREADS = 32 * (SK_CONSUMERS + 1);
 constexpr int SK_MAX_STAGES = 22;
 constexpr int SK_BURST = 4;  // units the producer issues back to back
-constexpr int SK_BAR_BYTES = 2 * 8 * SK_MAX_STAGES;
+constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 2);  // ring barriers + "parked" + "collected"
 constexpr int SK_RED_BYTES_PER_MT = SK_TILES * (SK_PHASES - 1) * 32 * 16;  // cross-phase exchange
+constexpr int SK_COLLECT_BYTES_PER_MT = SK_TILES * 32 * 16;               // other CTAs' fragments, summed
 
 enum : int { F_W4_SYM = 0, F_W4_ASYM = 1, F_MX = 2 };
 
@@ -142,6 +143,32 @@ struct Walk {
   }
 };
 
+// What a CTA does with panels it covers only in part. It parks at most one fragment per
+// tile (the panel whose end another CTA owns) and completes at most one panel (the one
+// whose end it owns); panels it covers whole are written directly.
+struct Handoff {
+  int park_panel, own_panel;  // -1: none
+  int b_first, b_last;        // CTAs contributing to own_panel (this CTA is b_last)
+  __device__ Handoff() : park_panel(-1), own_panel(-1), b_first(0), b_last(0) {}
+  __device__ Handoff(const Walk& w, int U, int C, int grid, int me) : park_panel(-1), own_panel(-1), b_first(0), b_last(0) {
+    // only the first and the last segment of a walk can be partial panels
+    for (int i = 0; i < w.nseg; i += (w.nseg > 1 ? w.nseg - 1 : 1)) {
+      int ua, len;
+      w.segment(i, C, &ua, &len);
+      const int p = ua / C, ch0 = ua - p * C;
+      if (ch0 == 0 && len == C) continue;  // whole panel
+      const int last = unit_owner(U, (p + 1) * C - 1, grid);
+      if (last == me) {
+        own_panel = p;
+        b_first = unit_owner(U, p * C, grid);
+        b_last = last;
+      } else {
+        park_panel = p;
+      }
+    }
+  }
+};
+
 template <int FMT, int GS>
 struct Groups;  // per-row decode constants of one unit: [0] for words 0-3, [1] for words 4-7
 
@@ -205,6 +232,13 @@ __device__ __forceinline__ uint32_t word_of(const uint4& a, const uint4& b, int 
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+// Signals the barrier without waiting for it (the producer half of a producer/consumer pair).
+__device__ __forceinline__ void named_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+constexpr int BAR_HANDED = 1;   // +tile: phases 1..3 have written their fragments (phase 0 waits)
+constexpr int BAR_TAKEN = 5;    // +tile: phase 0 has read them (phases 1..3 wait before rewriting)
+constexpr int BAR_XFILL = 9;    // all consumer warps: the activations are in shared memory
 
 template <int FMT, int GS, int MT, bool HOOK>
 __global__ void __launch_bounds__(SK_THREADS, 1)
@@ -218,19 +252,32 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
   uint8_t* sm_meta = sm_q + (size_t)stages * SK_STAGE_Q;
   uint8_t* sm_x = sm_meta + (size_t)stages * SK_META;
   uint8_t* sm_red = sm_x + (size_t)(a.xrows + 1) * a.xpitch;  // + one all-zero activation row
-  const uint32_t sm_bar = smem_u32(sm_red + MT * SK_RED_BYTES_PER_MT);
+  uint8_t* sm_collect = sm_red + MT * SK_RED_BYTES_PER_MT;
+  const uint32_t sm_bar = smem_u32(sm_collect + MT * SK_COLLECT_BYTES_PER_MT);
   auto full_bar = [&](int s) { return sm_bar + 8u * (uint32_t)s; };
   auto empty_bar = [&](int s) { return sm_bar + 8u * (uint32_t)(stages + s); };
+  const uint32_t parked_bar = sm_bar + 8u * (uint32_t)(2 * stages);      // 4 tile warps parked their fragment
+  const uint32_t collected_bar = parked_bar + 8u;                        // the other CTAs' fragments are summed
 
   const int grid = (int)gridDim.x;
   const int m0 = (int)blockIdx.y * a.xrows;  // first activation row of this pass
   const int mrows = min(a.xrows, a.M - m0);   // rows of this pass (the last may be short)
   const int C = a.C;
   const Walk walk(unit_begin(a.U, (int)blockIdx.x, grid), unit_begin(a.U, (int)blockIdx.x + 1, grid), C);
+  // parked fragment of (CTA, slot, tile): slot 0 when the panel is the CTA's first one
+  auto slot_of = [&](int which_cta, int tile_, int panel) {
+    const int slot = (unit_begin(a.U, which_cta, grid) / C == panel) ? 0 : 1;
+    return reinterpret_cast<float4*>(a.ws) +
+           ((((size_t)blockIdx.y * grid + which_cta) * 2 + slot) * SK_TILES + tile_) * MT * 32;
+  };
 
   if (tid < stages) {
     mbar_init(full_bar(tid), 33);  // lane 0's expect_tx arrive + one cp.async arrive per producer lane
     mbar_init(empty_bar(tid), SK_TILES);  // the four tile warps of the phase that consumes the stage
+    if (tid == 0) {
+      mbar_init(parked_bar, SK_TILES);
+      mbar_init(collected_bar, 1);
+    }
     mbar_init_fence();
   }
   if (tid == 32 * SK_CONSUMERS) tma_prefetch_desc(&tmap);
@@ -243,6 +290,69 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     // Units are issued in bursts of SK_BURST consecutive units (adjacent 128-byte
     // columns of the same rows): DRAM then sees 128*SK_BURST contiguous bytes per row at
     // once instead of isolated 128-byte reads, which is what keeps its pages busy.
+    // Besides loading, this warp does the CTA's hand-offs with other CTAs, so that no consumer
+    // warp ever waits for a round trip to L2: (1) once the four tile warps have parked their
+    // fragment it fences and bumps the tiles' counters; (2) for the panel this CTA completes it
+    // waits for the other CTAs' counters, adds their fragments in CTA order into shared memory
+    // and signals `collected`. (1) is polled between bursts, (2) once every unit is issued.
+    Handoff hand;  // worked out after the first burst is on its way
+    bool park_done = true, collect_done = true;
+    auto tile_live = [&](int panel, int t) { return panel * SK_ROWS + t * 16 < a.N; };
+    auto poll = [&](bool all_issued) {
+      if (!park_done && mbar_test(parked_bar, 0u)) {
+        __threadfence();  // the parked fragments are visible before the counters move
+        if (lane < SK_TILES && tile_live(hand.park_panel, lane))
+          atomicAdd(a.counters + ((size_t)blockIdx.y * a.P + hand.park_panel) * SK_TILES + lane, 1);
+        park_done = true;
+      }
+      if (!collect_done && all_issued) {  // reading the counters costs a trip to L2: not between bursts
+        int* cnt = a.counters + ((size_t)blockIdx.y * a.P + hand.own_panel) * SK_TILES;
+        bool ready = true;
+        if (lane < SK_TILES && tile_live(hand.own_panel, lane))
+          ready = *reinterpret_cast<volatile int*>(cnt + lane) >= hand.b_last - hand.b_first;
+        if (__all_sync(0xffffffffu, ready)) {
+          __threadfence();
+          constexpr int TB = MT == 1 ? SK_TILES : 2;  // tiles whose fragments are in flight together
+#pragma unroll 1
+          for (int t0 = 0; t0 < SK_TILES; t0 += TB) {
+            float4 sum[TB][MT];
+#pragma unroll
+            for (int t = 0; t < TB; ++t)
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) sum[t][mt] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int b = hand.b_first; b < hand.b_last; ++b) {  // fixed order: by CTA, never by arrival
+              float4 v[TB][MT];
+#pragma unroll
+              for (int t = 0; t < TB; ++t) {
+                const float4* theirs = slot_of(b, t0 + t, hand.own_panel);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt)
+                  v[t][mt] = tile_live(hand.own_panel, t0 + t) ? __ldcg(theirs + mt * 32 + lane)
+                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int t = 0; t < TB; ++t)
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                  sum[t][mt].x += v[t][mt].x;
+                  sum[t][mt].y += v[t][mt].y;
+                  sum[t][mt].z += v[t][mt].z;
+                  sum[t][mt].w += v[t][mt].w;
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < TB; ++t)
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt)
+                reinterpret_cast<float4*>(sm_collect)[((t0 + t) * MT + mt) * 32 + lane] = sum[t][mt];
+          }
+          if (lane < SK_TILES) cnt[lane] = 0;  // ready for the next launch
+          __syncwarp();
+          if (lane == 0) mbar_arrive(collected_bar);
+          collect_done = true;
+        }
+      }
+    };
     const int total = walk.u1 - walk.u0;
     int sw = 0, si = 0;            // ring slot of the next unit to wait for / to issue
     uint32_t phw = 0;              // parity of the wait cursor
@@ -293,6 +403,24 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
           r = 0;
         }
       }
+      if (j0 == 0) {
+        hand = Handoff(walk, a.U, C, grid, (int)blockIdx.x);
+        park_done = hand.park_panel < 0;
+        collect_done = hand.own_panel < 0;
+      }
+      poll(false);
+    }
+    {  // finish the hand-offs (bounded)
+      const long long t0 = clock64();
+      while (!(park_done && collect_done)) {
+        poll(true);
+        if (park_done && collect_done) break;
+        __nanosleep(100);
+        if (clock64() - t0 > kWaitLimitCycles) {
+          if (lane == 0) atomicExch(a.status, ST_STREAM_PANEL_TIMEOUT);
+          break;
+        }
+      }
     }
     return;
   }
@@ -314,7 +442,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     }
     for (int idx = tid; idx < cpr; idx += 32 * SK_CONSUMERS)
       *reinterpret_cast<uint4*>(sm_x + (size_t)a.xrows * a.xpitch + ((size_t)idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
-    named_barrier(5, 32 * SK_CONSUMERS);
+    named_barrier(BAR_XFILL, 32 * SK_CONSUMERS);
   }
 
   const int tile = wid & (SK_TILES - 1), phase = wid >> 2;
@@ -330,10 +458,6 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     xrow[mt] = smem_u32(sm_x) + (uint32_t)(xok[mt] ? g + 8 * mt : 0) * (uint32_t)a.xpitch + ((uint32_t)c << 4);
     xv[mt] = make_uint4(0u, 0u, 0u, 0u);
   }
-  const size_t cta = (size_t)blockIdx.y * grid + blockIdx.x;
-  auto slot_ptr = [&](size_t which_cta, int slot) {
-    return reinterpret_cast<float4*>(a.ws) + (((which_cta * 2 + slot) * SK_TILES + tile) * MT) * 32;
-  };
   const W4Consts kc = w4_consts();
   const int ra = tile * 16 + g;  // row inside the box; ra & 7 == g
   const uint32_t sw0 = ((uint32_t)(2 * c) ^ (uint32_t)g) << 4, sw1 = ((uint32_t)(2 * c + 1) ^ (uint32_t)g) << 4;
@@ -431,87 +555,63 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
       for (int i = 0; i < 4; ++i) out[mt][i] = acc[mt][0][i] + acc[mt][1][i];
     // the four phase warps of the tile: phases 1..3 hand their fragment to phase 0
     float4* red = reinterpret_cast<float4*>(sm_red) + (size_t)(tile * (SK_PHASES - 1)) * MT * 32;
+    // Phases 1..3 never wait for phase 0 here unless it is a whole segment behind: they
+    // write, signal and go on to the next segment while phase 0 sums and hands the result on.
     if (phase != 0) {
+      if (seg > 0) named_barrier(BAR_TAKEN + tile, 32 * SK_PHASES);  // phase 0 has read the previous fragments
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
         red[((phase - 1) * MT + mt) * 32 + lane] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
+      named_arrive(BAR_HANDED + tile, 32 * SK_PHASES);
+      continue;
     }
-    named_barrier(1 + tile, 32 * SK_PHASES);
-    if (phase == 0) {
+    named_barrier(BAR_HANDED + tile, 32 * SK_PHASES);
 #pragma unroll
-      for (int f = 0; f < SK_PHASES - 1; ++f)  // fixed order: phase 1, 2, 3
+    for (int f = 0; f < SK_PHASES - 1; ++f)  // fixed order: phase 1, 2, 3
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const float4 v = red[(f * MT + mt) * 32 + lane];
+        out[mt][0] += v.x;
+        out[mt][1] += v.y;
+        out[mt][2] += v.z;
+        out[mt][3] += v.w;
+      }
+    if (seg + 1 < walk.nseg) named_arrive(BAR_TAKEN + tile, 32 * SK_PHASES);
+    const bool whole = (ch0 == 0 && len == C);  // the whole K range was ours
+    const bool owner = !whole && unit_owner(a.U, (p + 1) * C - 1, grid) == (int)blockIdx.x;
+    const bool parks = !whole && !owner;
+    if (!live || !alive) {
+      if (parks && lane == 0) mbar_arrive(parked_bar);  // the count covers all four tiles
+      continue;
+    }
+
+    // (only phase-0 warps get here, with the tile's complete fragment for this segment)
+    bool write = whole;
+    if (!write) {
+      if (owner) {
+        // this CTA completes the panel: the producer warp has summed the others' fragments
+        if (!mbar_wait(collected_bar, 0u, a.status, ST_STREAM_PANEL_TIMEOUT)) {
+          alive = false;
+          continue;
+        }
+        const float4* others = reinterpret_cast<const float4*>(sm_collect) + (size_t)tile * MT * 32;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-          const float4 v = red[(f * MT + mt) * 32 + lane];
-          out[mt][0] += v.x;
-          out[mt][1] += v.y;
-          out[mt][2] += v.z;
-          out[mt][3] += v.w;
+          const float4 v = others[mt * 32 + lane];
+          out[mt][0] = v.x + out[mt][0];
+          out[mt][1] = v.y + out[mt][1];
+          out[mt][2] = v.z + out[mt][2];
+          out[mt][3] = v.w + out[mt][3];
         }
-    }
-    named_barrier(1 + tile, 32 * SK_PHASES);  // the exchange area may be reused
-    if (phase != 0 || !live || !alive) continue;
-
-    bool write = (ch0 == 0 && len == C);  // the whole K range was ours
-    if (!write) {
-      const int b_first = unit_owner(a.U, p * C, grid);
-      const int b_last = unit_owner(a.U, (p + 1) * C - 1, grid);
-      int* cnt = a.counters + ((size_t)blockIdx.y * a.P + p) * SK_TILES + tile;
-      if ((int)blockIdx.x != b_last) {
-        // park the fragment; the owner of the panel's end collects it
-        const int slot = (walk.u0 / C == p) ? 0 : 1;
-        float4* mine = slot_ptr(cta, slot);
+        write = true;
+      } else {
+        // park the fragment; the producer warp publishes it, the panel's owner collects it
+        float4* mine = slot_of((int)blockIdx.x, tile, p);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
           mine[mt * 32 + lane] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
         __syncwarp();
-        if (lane == 0) {
-          __threadfence();  // the warp's parked fragment is visible before the counter moves
-          atomicAdd(cnt, 1);
-        }
-      } else {
-        // owner: wait (bounded) until the b_last - b_first others have parked, add in CTA order
-        int ok = 1;
-        if (lane == 0) {
-          const long long t0 = clock64();
-          while (*reinterpret_cast<volatile int*>(cnt) < b_last - b_first) {
-            __nanosleep(64);
-            if (clock64() - t0 > kWaitLimitCycles) {
-              atomicExch(a.status, ST_STREAM_PANEL_TIMEOUT);
-              ok = 0;
-              break;
-            }
-          }
-          __threadfence();
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) {
-          alive = false;
-          continue;
-        }
-        float sum[MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) sum[mt][i] = 0.0f;
-        for (int b = b_first; b < b_last; ++b) {  // fixed order: by CTA, never by arrival
-          const int their_slot = (unit_begin(a.U, b, grid) / C == p) ? 0 : 1;
-          const float4* theirs = slot_ptr((size_t)blockIdx.y * grid + b, their_slot);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            const float4 v = __ldcg(theirs + mt * 32 + lane);
-            sum[mt][0] += v.x;
-            sum[mt][1] += v.y;
-            sum[mt][2] += v.z;
-            sum[mt][3] += v.w;
-          }
-        }
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) out[mt][i] = sum[mt][i] + out[mt][i];
-        if (lane == 0) *cnt = 0;  // ready for the next launch
-        write = true;
+        if (lane == 0) mbar_arrive(parked_bar);
       }
     }
     if (write) {
@@ -579,9 +679,11 @@ cudaError_t launch_fmt(const CUtensorMap& tmap, const StreamParams& sp, int mt, 
 
 constexpr int kSmemBudget = 232448 - 1024 /* alignment slack */ - SK_BAR_BYTES;
 // ring depth that fits beside `rows` activation rows (+ the zero row) and the exchange area
+constexpr int kMinStages = 7;  // a burst in flight and most of another being consumed
 int stages_for(int rows, int K) {
   const int mt = rows > 8 ? 2 : 1;
-  return (kSmemBudget - (rows + 1) * (K * 2 + 64) - mt * SK_RED_BYTES_PER_MT) / (SK_STAGE_Q + SK_META);
+  return (kSmemBudget - (rows + 1) * (K * 2 + 64) - mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT)) /
+         (SK_STAGE_Q + SK_META);
 }
 
 }  // namespace
@@ -592,7 +694,7 @@ bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, cons
   if (gs_or_0_for_mx != 0 && gs_or_0_for_mx != 32 && gs_or_0_for_mx != 64 && gs_or_0_for_mx != 128)
     return false;
   if (((uintptr_t)q | (uintptr_t)scales | (uintptr_t)x) & 15u) return false;
-  if (K > 65536 || stages_for(1, K) < 8) return false;  // one activation row must fit beside an 8-stage ring
+  if (K > 65536 || stages_for(1, K) < kMinStages) return false;  // one activation row must fit beside the shortest ring
   // 32-bit unit arithmetic: units * CTAs below 2^31 (>= 100 GB of packed weights on 148 SMs)
   if ((long long)((N + SK_ROWS - 1) / SK_ROWS) * (K / SK_KC) * 1024 >= (1LL << 31)) return false;
   return encode_tiled() != nullptr;
@@ -600,10 +702,10 @@ bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, cons
 
 void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan) {
   const int xpitch = K * 2 + 64;
-  // activation rows per pass: 16 if they leave room for an 8-stage ring, else 8, else fewer
+  // activation rows per pass: 16 if they leave room for the shortest ring, else 8, else fewer
   int rows = M < 16 ? M : 16;
-  if (rows > 8 && stages_for(rows, K) < 8) rows = 8;
-  while (rows > 1 && stages_for(rows, K) < 8) --rows;
+  if (rows > 8 && stages_for(rows, K) < kMinStages) rows = 8;
+  while (rows > 1 && stages_for(rows, K) < kMinStages) --rows;
   plan->rows_per_pass = rows;
   plan->mt = rows > 8 ? 2 : 1;
   plan->passes = (M + rows - 1) / rows;
@@ -615,7 +717,7 @@ void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan) {
   plan->grid_x = (int)(plan->U < sm_count ? plan->U : sm_count);
   plan->xpitch = xpitch;
   plan->smem = 1024 + (size_t)plan->stages * (SK_STAGE_Q + SK_META) + (size_t)(rows + 1) * xpitch +
-               (size_t)plan->mt * SK_RED_BYTES_PER_MT + SK_BAR_BYTES;
+               (size_t)plan->mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT) + SK_BAR_BYTES;
   plan->ws_bytes = (size_t)plan->passes * plan->grid_x * 2 * SK_TILES * plan->mt * 32 * sizeof(float4);
   plan->counter_ints = (size_t)plan->passes * plan->P * SK_TILES;
 }
