@@ -315,6 +315,14 @@ cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* ou
   while (lpp < p.wd && lpp < 32) lpp <<= 1;
   p.lpp = lpp;
   cudaError_t e;
+  if (attn_mma_supported(src, D, q, k_out, v_out)) {
+    e = attn_mma_launch(src, q, out, H, S, D, splits, ws, k_out, v_out, stream);
+    *launches = 1;
+    if (e != cudaSuccess || splits == 1) return e;
+    flash_combine_kernel<<<H, 128, 0, stream>>>(ws, out, splits, D);
+    *launches = 2;
+    return cudaGetLastError();
+  }
   switch (src.fmt) {
     case ATTN_FP16: e = launch_fmt<ATTN_FP16>(p, stream); break;
     case ATTN_W4_SYM: e = launch_fmt<ATTN_W4_SYM>(p, stream); break;

@@ -1,0 +1,529 @@
+// Split-S decode attention on the tensor pipe for the common head sizes
+// (D = 64 or 128; W4 / FP8 group size 32, 64 or 128; FP16): the fast form of
+// the reference's flash_*_phase1 kernels (include/w4/kvflash.cuh:73-199,
+// 202-288, 459-570, 598-723). attn_flash.cu keeps every other shape.
+//
+// grid = (heads, splits); a CTA owns a contiguous slice of one head's positions
+// and each of its 4 warps walks blocks of 16 positions with an online softmax.
+// Per block and warp:
+//
+//   scores = K q   mma.m16n8k16 with A = K (16 positions x 16 d per step), B = q in
+//                  every column. Lane (g, c) decodes the quarter c of rows g and
+//                  g + 8 in registers straight into A fragments - the k slots of a
+//                  step may hold any d as long as q is arranged the same way, so a
+//                  packed W4 word is used exactly as the decoder emits it.
+//   out^T += V^T p mma.m16n8k16 with A = V^T (16 d x 16 positions), B = p in every
+//                  column. A fragment registers pair two POSITIONS of one d; lane
+//                  (g, c) therefore loads positions 2c, 2c+1, 2c+8, 2c+9 of the d range
+//                  of g, interleaves the codes of two positions with one byte
+//                  permute per word and decodes both positions in each half2
+//                  operation (two scales / zero points per instruction). No shared
+//                  memory, no transposes, every cache byte is loaded once.
+//
+// Dequantised values are bit-identical to the host formats (the same decoders as
+// the GEMM kernels; FP8: the byte placed in a half is code * 2^-8, times 256 is
+// exact, times the scale rounds once). Sums are formed in a fixed order: lanes,
+// then warps, then splits - the same call gives the same bits, with or without the
+// dequantisation hooks, paged or contiguous.
+#include <math_constants.h>
+
+#include "w4b_common.cuh"
+#include "w4b_kernels.h"
+
+namespace w4b {
+namespace {
+
+constexpr int MA_WARPS = 4;
+constexpr int MA_THREADS = 32 * MA_WARPS;
+constexpr int MA_BLOCK = 16;  // positions per warp step
+
+struct MmaParams {
+  AttnSource src;
+  const __half* q;
+  __half* out;
+  float* ws;
+  __half* k_out;
+  __half* v_out;
+  int H, S, splits;
+  int gshift;  // log2(group size)
+  int wide;    // the hooks may be written 16 bytes at a time
+};
+
+__device__ __forceinline__ long long row_of(const AttnSource& s, int h, int t) {
+  const long long r = s.bt ? (long long)s.bt[t / s.page] * s.page + (t % s.page) : (long long)t;
+  return (long long)h * s.slab_rows + r;
+}
+
+// Decode constants for two rows at once: low half = first row, high half = second row.
+__device__ __forceinline__ W4Group w4_group2(__half s1, uint32_t z1, __half s2, uint32_t z2) {
+  W4Group g;
+  g.s2 = __halves2half2(s1, s2);
+  const uint32_t z = z1 | (z2 << 16);
+  g.za = u32_as_h2(z + 0x64006400u);         // 1024 + z
+  g.zb = u32_as_h2((z << 4) + 0xD400D400u);  // -(64 + z)
+  return g;
+}
+
+// FP8 E4M3 pair sitting in bits 15..8 and 31..24 of x (other bits arbitrary) -> the two
+// dequantised halves, each times its scale in s2.
+__device__ __forceinline__ __half2 dq_f8_pair(uint32_t x, __half2 s2) {
+  const uint32_t mag = (x >> 1) & 0x3F803F80u;
+  const uint32_t bits = and_or(x, 0x80008000u, mag);  // sign | exponent, mantissa: code * 2^-8
+  const __half2 v = __hmul2_rn(u32_as_h2(bits), u32_as_h2(0x5C005C00u));  // * 256, exact
+  return __hmul2_rn(v, s2);
+}
+
+__device__ __forceinline__ __half ldg_half(const __half* p) {
+  return __ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(p)));
+}
+
+// ---------------------------------------------------------------------------
+// Raw data of one block of 16 positions, as loaded by one lane.
+//   K side: rows g and g + 8, elements [E*c, E*c + E) with E = D/4.
+//   V side: rows 2c, 2c+1, 2c+8, 2c+9, elements [EV*g, EV*g + EV) with EV = D/8.
+// ---------------------------------------------------------------------------
+template <int FMT, int D>
+struct BlockData;
+
+template <int D>
+struct BlockData<ATTN_FP16, D> {
+  static constexpr int KU = D / 32, VU = D / 64;  // uint4 per row
+  uint4 k[2][KU];
+  uint4 v[4][VU];
+  __device__ __forceinline__ void load(const AttnSource& s, const long long rk[2], const long long rv[4], int g, int c,
+                                       int /*gshift*/) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int i = 0; i < KU; ++i)
+        k[r][i] = __ldg(reinterpret_cast<const uint4*>((const __half*)s.k + rk[r] * D + (D / 4) * c) + i);
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int i = 0; i < VU; ++i)
+        v[r][i] = __ldg(reinterpret_cast<const uint4*>((const __half*)s.v + rv[r] * D + (D / 8) * g) + i);
+  }
+};
+
+template <int D>
+struct BlockData<ATTN_F8, D> {
+  static constexpr int KW = D / 16, VW = D / 32;  // 32-bit words per row
+  uint32_t k[2][KW];
+  uint32_t v[4][VW];
+  __half ks[2], vs[4];
+  __device__ __forceinline__ void load(const AttnSource& s, const long long rk[2], const long long rv[4], int g, int c,
+                                       int gshift) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const uint8_t* p = (const uint8_t*)s.k + rk[r] * D + (D / 4) * c;
+      if (KW == 8) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+        k[r][0] = a.x, k[r][1] = a.y, k[r][2] = a.z, k[r][3] = a.w;
+        k[r][4 % KW] = b.x, k[r][5 % KW] = b.y, k[r][6 % KW] = b.z, k[r][7 % KW] = b.w;
+      } else {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+        k[r][0] = a.x, k[r][1] = a.y, k[r][2] = a.z, k[r][3] = a.w;
+      }
+      ks[r] = ldg_half(s.s_k + rk[r] * s.G + (((D / 4) * c) >> gshift));
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint8_t* p = (const uint8_t*)s.v + rv[r] * D + (D / 8) * g;
+      if (VW == 4) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+        v[r][0] = a.x, v[r][1] = a.y, v[r][2 % VW] = a.z, v[r][3 % VW] = a.w;
+      } else {
+        const uint2 a = __ldg(reinterpret_cast<const uint2*>(p));
+        v[r][0] = a.x, v[r][1] = a.y;
+      }
+      vs[r] = ldg_half(s.s_v + rv[r] * s.G + (((D / 8) * g) >> gshift));
+    }
+  }
+};
+
+template <int FMT, int D>
+struct BlockDataW4 {
+  static constexpr int KW = D / 32, VW = D / 64;  // packed words per row
+  static constexpr int WD = D / 8;                // words per cache row
+  uint32_t k[2][KW];
+  uint32_t v[4][VW];
+  __half ks[2], vs[4];
+  uint32_t kz[2], vz[4];  // zero points
+  __device__ __forceinline__ void load(const AttnSource& s, const long long rk[2], const long long rv[4], int g, int c,
+                                       int gshift) {
+    const int wG = words(s.G);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const uint32_t* p = (const uint32_t*)s.k + rk[r] * WD + KW * c;
+      if (KW == 4) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+        k[r][0] = a.x, k[r][1] = a.y, k[r][2 % KW] = a.z, k[r][3 % KW] = a.w;
+      } else {
+        const uint2 a = __ldg(reinterpret_cast<const uint2*>(p));
+        k[r][0] = a.x, k[r][1] = a.y;
+      }
+      const int grp = ((D / 4) * c) >> gshift;
+      ks[r] = ldg_half(s.s_k + rk[r] * s.G + grp);
+      kz[r] = FMT == ATTN_W4_ASYM ? ((__ldg(s.z_k + rk[r] * wG + (grp >> 3)) >> (4 * (grp & 7))) & 0xFu) : 8u;
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint32_t* p = (const uint32_t*)s.v + rv[r] * WD + VW * g;
+      if (VW == 2) {
+        const uint2 a = __ldg(reinterpret_cast<const uint2*>(p));
+        v[r][0] = a.x, v[r][1 % VW] = a.y;
+      } else {
+        v[r][0] = __ldg(p);
+      }
+      const int grp = ((D / 8) * g) >> gshift;
+      vs[r] = ldg_half(s.s_v + rv[r] * s.G + grp);
+      vz[r] = FMT == ATTN_W4_ASYM ? ((__ldg(s.z_v + rv[r] * wG + (grp >> 3)) >> (4 * (grp & 7))) & 0xFu) : 8u;
+    }
+  }
+};
+template <int D>
+struct BlockData<ATTN_W4_SYM, D> : BlockDataW4<ATTN_W4_SYM, D> {};
+template <int D>
+struct BlockData<ATTN_W4_ASYM, D> : BlockDataW4<ATTN_W4_ASYM, D> {};
+
+__device__ __forceinline__ uint4 unpair4(const __half2 p[4]) {  // (e, e+4) pairs -> 8 halves in order
+  uint4 r;
+  r.x = __byte_perm(h2_as_u32(p[0]), h2_as_u32(p[1]), 0x5410);
+  r.y = __byte_perm(h2_as_u32(p[2]), h2_as_u32(p[3]), 0x5410);
+  r.z = __byte_perm(h2_as_u32(p[0]), h2_as_u32(p[1]), 0x7632);
+  r.w = __byte_perm(h2_as_u32(p[2]), h2_as_u32(p[3]), 0x7632);
+  return r;
+}
+
+// Eight halves to dst (16-byte store when allowed).
+__device__ __forceinline__ void store8(__half* dst, uint4 v, bool wide) {
+  if (wide) {
+    *reinterpret_cast<uint4*>(dst) = v;
+  } else {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      dst[2 * i] = __ushort_as_half((unsigned short)(w[i] & 0xFFFFu));
+      dst[2 * i + 1] = __ushort_as_half((unsigned short)(w[i] >> 16));
+    }
+  }
+}
+
+template <int FMT, int D, bool HOOK>
+__global__ void __launch_bounds__(MA_THREADS) attn_mma_kernel(const MmaParams p) {
+  constexpr int E = D / 4;    // K elements per lane per row
+  constexpr int EV = D / 8;   // V elements per lane per row
+  constexpr int NQ = E / 8;   // q fragments (8 elements each) per lane
+  constexpr int NT = EV / 2;  // output tiles (16 d each... per lane: rows g and g+8)
+  __shared__ float sm_ml[MA_WARPS][2];
+  __shared__ float sm_acc[MA_WARPS][D];
+  const int h = blockIdx.x, sp = blockIdx.y;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int t0 = (int)((long long)p.S * sp / p.splits), t1 = (int)((long long)p.S * (sp + 1) / p.splits);
+  const float scale = rsqrtf((float)D);
+  const AttnSource& s = p.src;
+
+  // q of this lane's K quarter, in the pairing its K fragments use
+  uint4 qf[NQ];
+#pragma unroll
+  for (int i = 0; i < NQ; ++i) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q + (size_t)h * D + E * c) + i);
+    qf[i] = (FMT == ATTN_W4_SYM || FMT == ATTN_W4_ASYM) ? pair_permute(v) : v;
+  }
+
+  float m = -CUDART_INF_F, l = 0.0f;
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+  const W4Consts kc = w4_consts();
+
+  auto rows_of = [&](int tb, long long rk[2], long long rv[4]) {
+    const int last = t1 - 1;  // positions past the slice read a valid row and get weight 0
+    rk[0] = row_of(s, h, min(tb + g, last));
+    rk[1] = row_of(s, h, min(tb + g + 8, last));
+    rv[0] = row_of(s, h, min(tb + 2 * c, last));
+    rv[1] = row_of(s, h, min(tb + 2 * c + 1, last));
+    rv[2] = row_of(s, h, min(tb + 2 * c + 8, last));
+    rv[3] = row_of(s, h, min(tb + 2 * c + 9, last));
+  };
+
+  const int step = MA_WARPS * MA_BLOCK;
+  int tb = t0 + wid * MA_BLOCK;
+  BlockData<FMT, D> nxt;
+  if (tb < t1) {
+    long long rk[2], rv[4];
+    rows_of(tb, rk, rv);
+    nxt.load(s, rk, rv, g, c, p.gshift);
+  }
+  for (; tb < t1; tb += step) {
+    const BlockData<FMT, D> cur = nxt;
+    if (tb + step < t1) {  // the next block's loads fly while this one is computed
+      long long rk[2], rv[4];
+      rows_of(tb + step, rk, rv);
+      nxt.load(s, rk, rv, g, c, p.gshift);
+    }
+
+    // ---------------- scores of rows g and g + 8 ----------------
+    float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+    if constexpr (FMT == ATTN_FP16) {
+#pragma unroll
+      for (int i = 0; i < NQ; ++i) {
+        const uint32_t f0[4] = {cur.k[0][i].x, cur.k[1][i].x, cur.k[0][i].y, cur.k[1][i].y};
+        const uint32_t f1[4] = {cur.k[0][i].z, cur.k[1][i].z, cur.k[0][i].w, cur.k[1][i].w};
+        mma_16816(sa, f0, qf[i].x, qf[i].y);
+        mma_16816(sb, f1, qf[i].z, qf[i].w);
+      }
+    } else if constexpr (FMT == ATTN_F8) {
+      const __half2 s0 = __half2half2(cur.ks[0]), s1 = __half2half2(cur.ks[1]);
+#pragma unroll
+      for (int i = 0; i < NQ; ++i) {  // 8 bytes = 2 words per row per fragment
+        __half2 a[4], b[4];
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          const uint32_t x0 = cur.k[0][2 * i + w], x1 = cur.k[1][2 * i + w];
+          a[2 * w] = dq_f8_pair(__byte_perm(x0, 0, 0x1404), s0);      // bytes 0, 1
+          a[2 * w + 1] = dq_f8_pair(__byte_perm(x0, 0, 0x3424), s0);  // bytes 2, 3
+          b[2 * w] = dq_f8_pair(__byte_perm(x1, 0, 0x1404), s1);
+          b[2 * w + 1] = dq_f8_pair(__byte_perm(x1, 0, 0x3424), s1);
+        }
+        if (HOOK && p.k_out) {
+          const int d0 = E * c + 8 * i;
+          uint4 ua, ub;
+          ua.x = h2_as_u32(a[0]), ua.y = h2_as_u32(a[1]), ua.z = h2_as_u32(a[2]), ua.w = h2_as_u32(a[3]);
+          ub.x = h2_as_u32(b[0]), ub.y = h2_as_u32(b[1]), ub.z = h2_as_u32(b[2]), ub.w = h2_as_u32(b[3]);
+          if (tb + g < t1) store8(p.k_out + ((size_t)h * p.S + tb + g) * D + d0, ua, p.wide);
+          if (tb + g + 8 < t1) store8(p.k_out + ((size_t)h * p.S + tb + g + 8) * D + d0, ub, p.wide);
+        }
+        const uint32_t f0[4] = {h2_as_u32(a[0]), h2_as_u32(b[0]), h2_as_u32(a[1]), h2_as_u32(b[1])};
+        const uint32_t f1[4] = {h2_as_u32(a[2]), h2_as_u32(b[2]), h2_as_u32(a[3]), h2_as_u32(b[3])};
+        mma_16816(sa, f0, qf[i].x, qf[i].y);
+        mma_16816(sb, f1, qf[i].z, qf[i].w);
+      }
+    } else {
+      const W4Group ga = w4_group(cur.ks[0], cur.kz[0]), gb = w4_group(cur.ks[1], cur.kz[1]);
+#pragma unroll
+      for (int i = 0; i < NQ; ++i) {
+        __half2 a[4], b[4];
+        dq_w4_word(cur.k[0][i], ga, kc, a);
+        dq_w4_word(cur.k[1][i], gb, kc, b);
+        if (HOOK && p.k_out) {
+          const int d0 = E * c + 8 * i;
+          if (tb + g < t1) store8(p.k_out + ((size_t)h * p.S + tb + g) * D + d0, unpair4(a), p.wide);
+          if (tb + g + 8 < t1) store8(p.k_out + ((size_t)h * p.S + tb + g + 8) * D + d0, unpair4(b), p.wide);
+        }
+        const uint32_t f0[4] = {h2_as_u32(a[0]), h2_as_u32(b[0]), h2_as_u32(a[1]), h2_as_u32(b[1])};
+        const uint32_t f1[4] = {h2_as_u32(a[2]), h2_as_u32(b[2]), h2_as_u32(a[3]), h2_as_u32(b[3])};
+        mma_16816(sa, f0, qf[i].x, qf[i].y);
+        mma_16816(sb, f1, qf[i].z, qf[i].w);
+      }
+    }
+    // the MMA has summed the four lanes' quarters; every column of the product holds the score
+    float s0 = sa[0] + sb[0], s1 = sa[2] + sb[2];
+    s0 = (tb + g < t1) ? s0 * scale : -CUDART_INF_F;
+    s1 = (tb + g + 8 < t1) ? s1 * scale : -CUDART_INF_F;
+
+    // ---------------- online softmax over the block ----------------
+    float bm = fmaxf(s0, s1);
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
+    if (bm > m) {  // the same decision in every lane
+      const float corr = __expf(m - bm);  // m = -inf on the first block: 0
+      l *= corr;
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] *= corr;
+      m = bm;
+    }
+    // weights as FP16 (the MMA's input type); the denominator adds the same rounded values
+    const __half2 pp = __floats2half2_rn(__expf(s0 - m), __expf(s1 - m));  // (p[g], p[g+8])
+    float ps = __low2float(pp) + __high2float(pp);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+    l += ps;
+    const uint32_t pu = __shfl_sync(0xffffffffu, h2_as_u32(pp), 8 * c);      // positions 2c, 2c+8
+    const uint32_t pv = __shfl_sync(0xffffffffu, h2_as_u32(pp), 8 * c + 4);  // positions 2c+1, 2c+9
+    const uint32_t pb0 = __byte_perm(pu, pv, 0x5410);                        // (p[2c], p[2c+1])
+    const uint32_t pb1 = __byte_perm(pu, pv, 0x7632);                        // (p[2c+8], p[2c+9])
+
+    // ---------------- V^T fragments: element e of rows (2c, 2c+1) and of rows (2c+8, 2c+9) ----------------
+    uint32_t v12[EV], v34[EV];
+    if constexpr (FMT == ATTN_FP16) {
+#pragma unroll
+      for (int e = 0; e < EV; e += 2) {
+        const uint4& r0 = cur.v[0][e / 8];
+        const uint4& r1 = cur.v[1][e / 8];
+        const uint4& r2 = cur.v[2][e / 8];
+        const uint4& r3 = cur.v[3][e / 8];
+        const int w = (e / 2) & 3;
+        const uint32_t x0 = w == 0 ? r0.x : (w == 1 ? r0.y : (w == 2 ? r0.z : r0.w));
+        const uint32_t x1 = w == 0 ? r1.x : (w == 1 ? r1.y : (w == 2 ? r1.z : r1.w));
+        const uint32_t x2 = w == 0 ? r2.x : (w == 1 ? r2.y : (w == 2 ? r2.z : r2.w));
+        const uint32_t x3 = w == 0 ? r3.x : (w == 1 ? r3.y : (w == 2 ? r3.z : r3.w));
+        v12[e] = __byte_perm(x0, x1, 0x5410);
+        v12[e + 1] = __byte_perm(x0, x1, 0x7632);
+        v34[e] = __byte_perm(x2, x3, 0x5410);
+        v34[e + 1] = __byte_perm(x2, x3, 0x7632);
+      }
+    } else if constexpr (FMT == ATTN_F8) {
+      const __half2 s12 = __halves2half2(cur.vs[0], cur.vs[1]), s34 = __halves2half2(cur.vs[2], cur.vs[3]);
+#pragma unroll
+      for (int e = 0; e < EV; ++e) {
+        const int w = e >> 2, b = e & 3;
+        // byte b of the first row to byte 1, byte b of the second row to byte 3
+        const uint32_t sel = b == 0 ? 0x4000u : (b == 1 ? 0x5010u : (b == 2 ? 0x6020u : 0x7030u));
+        v12[e] = h2_as_u32(dq_f8_pair(__byte_perm(cur.v[0][w], cur.v[1][w], sel), s12));
+        v34[e] = h2_as_u32(dq_f8_pair(__byte_perm(cur.v[2][w], cur.v[3][w], sel), s34));
+      }
+    } else {
+      const W4Group g12 = w4_group2(cur.vs[0], cur.vz[0], cur.vs[1], cur.vz[1]);
+      const W4Group g34 = w4_group2(cur.vs[2], cur.vz[2], cur.vs[3], cur.vz[3]);
+#pragma unroll
+      for (int w = 0; w < EV / 8; ++w) {
+        // codes 0..3 of both rows in one word, codes 4..7 in another: the word decoder then
+        // returns (row A code n, row B code n) pairs
+        __half2 lo[4], hi[4];
+        dq_w4_word(__byte_perm(cur.v[0][w], cur.v[1][w], 0x5410), g12, kc, lo);  // codes 0,1,2,3 (order 0,1,2,3)
+        dq_w4_word(__byte_perm(cur.v[0][w], cur.v[1][w], 0x7632), g12, kc, hi);
+        // dq_w4_word's out[i] pairs code i of the low half with code i of the high half:
+        // out[0] = code 0, out[1] = code 1, out[2] = code 2, out[3] = code 3 of each row
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v12[8 * w + i] = h2_as_u32(lo[i]);
+          v12[8 * w + 4 + i] = h2_as_u32(hi[i]);
+        }
+        dq_w4_word(__byte_perm(cur.v[2][w], cur.v[3][w], 0x5410), g34, kc, lo);
+        dq_w4_word(__byte_perm(cur.v[2][w], cur.v[3][w], 0x7632), g34, kc, hi);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v34[8 * w + i] = h2_as_u32(lo[i]);
+          v34[8 * w + 4 + i] = h2_as_u32(hi[i]);
+        }
+      }
+    }
+    if (HOOK && p.v_out && FMT != ATTN_FP16) {
+      // row 2c (+8): the low halves of v12 (v34); row 2c+1 (+9): the high halves
+#pragma unroll
+      for (int e0 = 0; e0 < EV; e0 += 8) {
+        uint4 a, b, cc, d;
+        a.x = __byte_perm(v12[e0], v12[e0 + 1], 0x5410), a.y = __byte_perm(v12[e0 + 2], v12[e0 + 3], 0x5410);
+        a.z = __byte_perm(v12[e0 + 4], v12[e0 + 5], 0x5410), a.w = __byte_perm(v12[e0 + 6], v12[e0 + 7], 0x5410);
+        b.x = __byte_perm(v12[e0], v12[e0 + 1], 0x7632), b.y = __byte_perm(v12[e0 + 2], v12[e0 + 3], 0x7632);
+        b.z = __byte_perm(v12[e0 + 4], v12[e0 + 5], 0x7632), b.w = __byte_perm(v12[e0 + 6], v12[e0 + 7], 0x7632);
+        cc.x = __byte_perm(v34[e0], v34[e0 + 1], 0x5410), cc.y = __byte_perm(v34[e0 + 2], v34[e0 + 3], 0x5410);
+        cc.z = __byte_perm(v34[e0 + 4], v34[e0 + 5], 0x5410), cc.w = __byte_perm(v34[e0 + 6], v34[e0 + 7], 0x5410);
+        d.x = __byte_perm(v34[e0], v34[e0 + 1], 0x7632), d.y = __byte_perm(v34[e0 + 2], v34[e0 + 3], 0x7632);
+        d.z = __byte_perm(v34[e0 + 4], v34[e0 + 5], 0x7632), d.w = __byte_perm(v34[e0 + 6], v34[e0 + 7], 0x7632);
+        const int d0 = EV * g + e0;
+        const size_t base = ((size_t)h * p.S + tb) * D + d0;
+        if (tb + 2 * c < t1) store8(p.v_out + base + (size_t)(2 * c) * D, a, p.wide);
+        if (tb + 2 * c + 1 < t1) store8(p.v_out + base + (size_t)(2 * c + 1) * D, b, p.wide);
+        if (tb + 2 * c + 8 < t1) store8(p.v_out + base + (size_t)(2 * c + 8) * D, cc, p.wide);
+        if (tb + 2 * c + 9 < t1) store8(p.v_out + base + (size_t)(2 * c + 9) * D, d, p.wide);
+      }
+    }
+    // out^T tile j: row g <-> d = EV*g + j, row g + 8 <-> d = EV*g + NT + j
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      const uint32_t f[4] = {v12[j], v12[j + NT], v34[j], v34[j + NT]};
+      mma_16816(acc[j], f, pb0, pb1);
+    }
+  }
+
+  // ---- warps of the CTA, merged in warp order; every column of acc holds the same value ----
+  if (lane == 0) {
+    sm_ml[wid][0] = m;
+    sm_ml[wid][1] = l;
+  }
+  if (c == 0) {
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      sm_acc[wid][EV * g + j] = acc[j][0];
+      sm_acc[wid][EV * g + NT + j] = acc[j][2];
+    }
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += MA_THREADS) {
+    float mm = sm_ml[0][0], ll = sm_ml[0][1], a = sm_acc[0][d];
+#pragma unroll
+    for (int w = 1; w < MA_WARPS; ++w) {
+      const float m2 = sm_ml[w][0], l2 = sm_ml[w][1], a2 = sm_acc[w][d];
+      const float mn = fmaxf(mm, m2);
+      const float fa = (mm == -CUDART_INF_F) ? 0.0f : __expf(mm - mn);
+      const float fb = (m2 == -CUDART_INF_F) ? 0.0f : __expf(m2 - mn);
+      ll = ll * fa + l2 * fb;
+      a = a * fa + a2 * fb;
+      mm = mn;
+    }
+    if (p.splits == 1) {
+      p.out[(size_t)h * D + d] = __float2half_rn(a / ll);
+    } else {
+      float* part = p.ws + ((size_t)h * p.splits + sp) * (size_t)(D + 2);
+      if (d == 0) {
+        part[0] = mm;
+        part[1] = ll;
+      }
+      part[2 + d] = a;
+    }
+  }
+}
+
+template <int FMT, int D>
+cudaError_t launch_d(const MmaParams& p, cudaStream_t stream) {
+  const dim3 grid((unsigned)p.H, (unsigned)p.splits);
+  if (p.k_out || p.v_out)
+    attn_mma_kernel<FMT, D, true><<<grid, MA_THREADS, 0, stream>>>(p);
+  else
+    attn_mma_kernel<FMT, D, false><<<grid, MA_THREADS, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <int FMT>
+cudaError_t launch_fmt(const MmaParams& p, int D, cudaStream_t stream) {
+  return D == 128 ? launch_d<FMT, 128>(p, stream) : launch_d<FMT, 64>(p, stream);
+}
+
+}  // namespace
+
+bool attn_mma_supported(const AttnSource& src, int D, const void* q, const void* k_out, const void* v_out) {
+  if (D != 64 && D != 128) return false;
+  if (src.fmt != ATTN_FP16) {
+    if (src.gs != 32 && src.gs != 64 && src.gs != 128) return false;
+    if (src.gs > D || src.G * src.gs != D) return false;
+  }
+  if (((uintptr_t)src.k | (uintptr_t)src.v | (uintptr_t)q) & 15u) return false;
+  (void)k_out;
+  (void)v_out;
+  return true;
+}
+
+// One pass over the cache: partial (m, l, acc) per (head, split) into ws, or the output itself
+// when splits == 1. The caller runs the split combine.
+cudaError_t attn_mma_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
+                            float* ws, __half* k_out, __half* v_out, cudaStream_t stream) {
+  MmaParams p;
+  p.src = src;
+  p.q = q;
+  p.out = out;
+  p.ws = ws;
+  p.k_out = k_out;
+  p.v_out = v_out;
+  p.H = H;
+  p.S = S;
+  p.splits = splits;
+  p.gshift = src.gs == 128 ? 7 : (src.gs == 64 ? 6 : 5);
+  p.wide = ((((uintptr_t)k_out | (uintptr_t)v_out) & 15u) == 0) ? 1 : 0;
+  switch (src.fmt) {
+    case ATTN_FP16: return launch_fmt<ATTN_FP16>(p, D, stream);
+    case ATTN_W4_SYM: return launch_fmt<ATTN_W4_SYM>(p, D, stream);
+    case ATTN_W4_ASYM: return launch_fmt<ATTN_W4_ASYM>(p, D, stream);
+    default: return launch_fmt<ATTN_F8>(p, D, stream);
+  }
+}
+
+}  // namespace w4b

@@ -80,4 +80,11 @@ size_t attn_flash_ws_bytes(int H, int D, int splits);
 cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
                               float* ws, __half* k_out, __half* v_out, cudaStream_t stream, int* launches);
 
+// ---- attn_mma.cu ------------------------------------------------------------
+// The tensor-pipe form of the flash pass for D = 64 / 128 and group sizes 32 / 64 / 128;
+// same workspace layout and split combine as attn_flash.cu.
+bool attn_mma_supported(const AttnSource& src, int D, const void* q, const void* k_out, const void* v_out);
+cudaError_t attn_mma_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
+                            float* ws, __half* k_out, __half* v_out, cudaStream_t stream);
+
 }  // namespace w4b
