@@ -284,9 +284,12 @@ cudaError_t launch_fmt(const FlashParams& p, cudaStream_t stream) {
 }  // namespace
 
 int attn_flash_splits(int H, int S, int sm_count) {
-  // enough CTAs for ~4 per SM, slices of at least FA_MIN_SPLIT positions
-  long long want = (4LL * sm_count + H - 1) / H;
-  const long long cap = (S + FA_MIN_SPLIT - 1) / FA_MIN_SPLIT;
+  // About eight waves of CTAs at four resident CTAs per SM (a partial last wave then costs
+  // little). Slices of at least 256 positions (four steps per warp) while that still gives
+  // every SM four CTAs, else of at least FA_MIN_SPLIT.
+  long long want = (32LL * sm_count + H - 1) / H;
+  long long cap = (S + 255) / 256;
+  if (cap * H < 4LL * sm_count) cap = (S + FA_MIN_SPLIT - 1) / FA_MIN_SPLIT;
   if (want > cap) want = cap;
   if (want > 65535) want = 65535;
   if (want < 1) want = 1;

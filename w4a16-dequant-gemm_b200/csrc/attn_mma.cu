@@ -49,10 +49,21 @@ struct MmaParams {
   int wide;    // the hooks may be written 16 bytes at a time
 };
 
-__device__ __forceinline__ long long row_of(const AttnSource& s, int h, int t) {
-  const long long r = s.bt ? (long long)s.bt[t / s.page] * s.page + (t % s.page) : (long long)t;
-  return (long long)h * s.slab_rows + r;
+// Row of logical position t inside its head's slab.
+__device__ __forceinline__ int row_of(const AttnSource& s, int t) {
+  return s.bt ? s.bt[t / s.page] * s.page + (t % s.page) : t;
 }
+
+// The arrays of one head (rows are then indexed with 32-bit multiplies by constant strides).
+struct HeadBase {
+  const uint8_t* k;
+  const uint8_t* v;
+  const __half* sk;
+  const __half* sv;
+  const uint32_t* zk;
+  const uint32_t* zv;
+  int G, wG;
+};
 
 // Decode constants for two rows at once: low half = first row, high half = second row.
 __device__ __forceinline__ W4Group w4_group2(__half s1, uint32_t z1, __half s2, uint32_t z2) {
@@ -90,18 +101,18 @@ struct BlockData<ATTN_FP16, D> {
   static constexpr int KU = D / 32, VU = D / 64;  // uint4 per row
   uint4 k[2][KU];
   uint4 v[4][VU];
-  __device__ __forceinline__ void load(const AttnSource& s, const long long rk[2], const long long rv[4], int g, int c,
+  __device__ __forceinline__ void load(const HeadBase& s, const int rk[2], const int rv[4], int g, int c,
                                        int /*gshift*/) {
 #pragma unroll
     for (int r = 0; r < 2; ++r)
 #pragma unroll
       for (int i = 0; i < KU; ++i)
-        k[r][i] = __ldg(reinterpret_cast<const uint4*>((const __half*)s.k + rk[r] * D + (D / 4) * c) + i);
+        k[r][i] = __ldg(reinterpret_cast<const uint4*>(s.k + (size_t)(unsigned)rk[r] * (2 * D) + (D / 2) * c) + i);
 #pragma unroll
     for (int r = 0; r < 4; ++r)
 #pragma unroll
       for (int i = 0; i < VU; ++i)
-        v[r][i] = __ldg(reinterpret_cast<const uint4*>((const __half*)s.v + rv[r] * D + (D / 8) * g) + i);
+        v[r][i] = __ldg(reinterpret_cast<const uint4*>(s.v + (size_t)(unsigned)rv[r] * (2 * D) + (D / 4) * g) + i);
   }
 };
 
@@ -111,11 +122,11 @@ struct BlockData<ATTN_F8, D> {
   uint32_t k[2][KW];
   uint32_t v[4][VW];
   __half ks[2], vs[4];
-  __device__ __forceinline__ void load(const AttnSource& s, const long long rk[2], const long long rv[4], int g, int c,
+  __device__ __forceinline__ void load(const HeadBase& s, const int rk[2], const int rv[4], int g, int c,
                                        int gshift) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      const uint8_t* p = (const uint8_t*)s.k + rk[r] * D + (D / 4) * c;
+      const uint8_t* p = s.k + (size_t)(unsigned)rk[r] * D + (D / 4) * c;
       if (KW == 8) {
         const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)), b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
         k[r][0] = a.x, k[r][1] = a.y, k[r][2] = a.z, k[r][3] = a.w;
@@ -124,11 +135,11 @@ struct BlockData<ATTN_F8, D> {
         const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
         k[r][0] = a.x, k[r][1] = a.y, k[r][2] = a.z, k[r][3] = a.w;
       }
-      ks[r] = ldg_half(s.s_k + rk[r] * s.G + (((D / 4) * c) >> gshift));
+      ks[r] = ldg_half(s.sk + (size_t)(unsigned)(rk[r] * s.G + (((D / 4) * c) >> gshift)));
     }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const uint8_t* p = (const uint8_t*)s.v + rv[r] * D + (D / 8) * g;
+      const uint8_t* p = s.v + (size_t)(unsigned)rv[r] * D + (D / 8) * g;
       if (VW == 4) {
         const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
         v[r][0] = a.x, v[r][1] = a.y, v[r][2 % VW] = a.z, v[r][3 % VW] = a.w;
@@ -136,7 +147,7 @@ struct BlockData<ATTN_F8, D> {
         const uint2 a = __ldg(reinterpret_cast<const uint2*>(p));
         v[r][0] = a.x, v[r][1] = a.y;
       }
-      vs[r] = ldg_half(s.s_v + rv[r] * s.G + (((D / 8) * g) >> gshift));
+      vs[r] = ldg_half(s.sv + (size_t)(unsigned)(rv[r] * s.G + (((D / 8) * g) >> gshift)));
     }
   }
 };
@@ -149,12 +160,11 @@ struct BlockDataW4 {
   uint32_t v[4][VW];
   __half ks[2], vs[4];
   uint32_t kz[2], vz[4];  // zero points
-  __device__ __forceinline__ void load(const AttnSource& s, const long long rk[2], const long long rv[4], int g, int c,
+  __device__ __forceinline__ void load(const HeadBase& s, const int rk[2], const int rv[4], int g, int c,
                                        int gshift) {
-    const int wG = words(s.G);
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      const uint32_t* p = (const uint32_t*)s.k + rk[r] * WD + KW * c;
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(s.k + (size_t)(unsigned)rk[r] * (WD * 4)) + KW * c;
       if (KW == 4) {
         const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
         k[r][0] = a.x, k[r][1] = a.y, k[r][2 % KW] = a.z, k[r][3 % KW] = a.w;
@@ -163,12 +173,13 @@ struct BlockDataW4 {
         k[r][0] = a.x, k[r][1] = a.y;
       }
       const int grp = ((D / 4) * c) >> gshift;
-      ks[r] = ldg_half(s.s_k + rk[r] * s.G + grp);
-      kz[r] = FMT == ATTN_W4_ASYM ? ((__ldg(s.z_k + rk[r] * wG + (grp >> 3)) >> (4 * (grp & 7))) & 0xFu) : 8u;
+      ks[r] = ldg_half(s.sk + (size_t)(unsigned)(rk[r] * s.G + grp));
+      kz[r] = FMT == ATTN_W4_ASYM ? ((__ldg(s.zk + (size_t)(unsigned)(rk[r] * s.wG + (grp >> 3))) >> (4 * (grp & 7))) & 0xFu)
+                                  : 8u;
     }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
-      const uint32_t* p = (const uint32_t*)s.v + rv[r] * WD + VW * g;
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(s.v + (size_t)(unsigned)rv[r] * (WD * 4)) + VW * g;
       if (VW == 2) {
         const uint2 a = __ldg(reinterpret_cast<const uint2*>(p));
         v[r][0] = a.x, v[r][1 % VW] = a.y;
@@ -176,8 +187,9 @@ struct BlockDataW4 {
         v[r][0] = __ldg(p);
       }
       const int grp = ((D / 8) * g) >> gshift;
-      vs[r] = ldg_half(s.s_v + rv[r] * s.G + grp);
-      vz[r] = FMT == ATTN_W4_ASYM ? ((__ldg(s.z_v + rv[r] * wG + (grp >> 3)) >> (4 * (grp & 7))) & 0xFu) : 8u;
+      vs[r] = ldg_half(s.sv + (size_t)(unsigned)(rv[r] * s.G + grp));
+      vz[r] = FMT == ATTN_W4_ASYM ? ((__ldg(s.zv + (size_t)(unsigned)(rv[r] * s.wG + (grp >> 3))) >> (4 * (grp & 7))) & 0xFu)
+                                  : 8u;
     }
   }
 };
@@ -210,7 +222,7 @@ __device__ __forceinline__ void store8(__half* dst, uint4 v, bool wide) {
 }
 
 template <int FMT, int D, bool HOOK>
-__global__ void __launch_bounds__(MA_THREADS) attn_mma_kernel(const MmaParams p) {
+__global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (FMT == ATTN_F8 ? 3 : 4)) attn_mma_kernel(const MmaParams p) {
   constexpr int E = D / 4;    // K elements per lane per row
   constexpr int EV = D / 8;   // V elements per lane per row
   constexpr int NQ = E / 8;   // q fragments (8 elements each) per lane
@@ -220,9 +232,25 @@ __global__ void __launch_bounds__(MA_THREADS) attn_mma_kernel(const MmaParams p)
   const int h = blockIdx.x, sp = blockIdx.y;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const int t0 = (int)((long long)p.S * sp / p.splits), t1 = (int)((long long)p.S * (sp + 1) / p.splits);
+  // slices are cut at multiples of 64 positions: the four warps of a CTA get the same number of blocks
+  const int units = (p.S + MA_WARPS * MA_BLOCK - 1) / (MA_WARPS * MA_BLOCK);
+  const int t0 = MA_WARPS * MA_BLOCK * (int)((long long)units * sp / p.splits);
+  const int t1 = min(p.S, MA_WARPS * MA_BLOCK * (int)((long long)units * (sp + 1) / p.splits));
   const float scale = rsqrtf((float)D);
   const AttnSource& s = p.src;
+  HeadBase hb;
+  {
+    const size_t slab = (size_t)h * (size_t)s.slab_rows;
+    const size_t row_bytes = FMT == ATTN_FP16 ? 2 * D : (FMT == ATTN_F8 ? D : D / 2);
+    hb.k = reinterpret_cast<const uint8_t*>(s.k) + slab * row_bytes;
+    hb.v = reinterpret_cast<const uint8_t*>(s.v) + slab * row_bytes;
+    hb.G = s.G;
+    hb.wG = words(s.G);
+    hb.sk = s.s_k ? s.s_k + slab * s.G : nullptr;
+    hb.sv = s.s_v ? s.s_v + slab * s.G : nullptr;
+    hb.zk = s.z_k ? s.z_k + slab * hb.wG : nullptr;
+    hb.zv = s.z_v ? s.z_v + slab * hb.wG : nullptr;
+  }
 
   // q of this lane's K quarter, in the pairing its K fragments use
   uint4 qf[NQ];
@@ -240,31 +268,19 @@ __global__ void __launch_bounds__(MA_THREADS) attn_mma_kernel(const MmaParams p)
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
   const W4Consts kc = w4_consts();
 
-  auto rows_of = [&](int tb, long long rk[2], long long rv[4]) {
+  auto fetch = [&](BlockData<FMT, D>& blk, int tb) {
     const int last = t1 - 1;  // positions past the slice read a valid row and get weight 0
-    rk[0] = row_of(s, h, min(tb + g, last));
-    rk[1] = row_of(s, h, min(tb + g + 8, last));
-    rv[0] = row_of(s, h, min(tb + 2 * c, last));
-    rv[1] = row_of(s, h, min(tb + 2 * c + 1, last));
-    rv[2] = row_of(s, h, min(tb + 2 * c + 8, last));
-    rv[3] = row_of(s, h, min(tb + 2 * c + 9, last));
+    int rk[2], rv[4];
+    rk[0] = row_of(s, min(tb + g, last));
+    rk[1] = row_of(s, min(tb + g + 8, last));
+    rv[0] = row_of(s, min(tb + 2 * c, last));
+    rv[1] = row_of(s, min(tb + 2 * c + 1, last));
+    rv[2] = row_of(s, min(tb + 2 * c + 8, last));
+    rv[3] = row_of(s, min(tb + 2 * c + 9, last));
+    blk.load(hb, rk, rv, g, c, p.gshift);
   };
 
-  const int step = MA_WARPS * MA_BLOCK;
-  int tb = t0 + wid * MA_BLOCK;
-  BlockData<FMT, D> nxt;
-  if (tb < t1) {
-    long long rk[2], rv[4];
-    rows_of(tb, rk, rv);
-    nxt.load(s, rk, rv, g, c, p.gshift);
-  }
-  for (; tb < t1; tb += step) {
-    const BlockData<FMT, D> cur = nxt;
-    if (tb + step < t1) {  // the next block's loads fly while this one is computed
-      long long rk[2], rv[4];
-      rows_of(tb + step, rk, rv);
-      nxt.load(s, rk, rv, g, c, p.gshift);
-    }
+  auto compute = [&](const BlockData<FMT, D>& cur, int tb) {
 
     // ---------------- scores of rows g and g + 8 ----------------
     float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
@@ -330,7 +346,7 @@ __global__ void __launch_bounds__(MA_THREADS) attn_mma_kernel(const MmaParams p)
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
-    if (bm > m) {  // the same decision in every lane
+    if (__any_sync(0xffffffffu, bm > m)) {  // the same decision in every lane; rare after the first blocks
       const float corr = __expf(m - bm);  // m = -inf on the first block: 0
       l *= corr;
 #pragma unroll
@@ -433,6 +449,21 @@ __global__ void __launch_bounds__(MA_THREADS) attn_mma_kernel(const MmaParams p)
       const uint32_t f[4] = {v12[j], v12[j + NT], v34[j], v34[j + NT]};
       mma_16816(acc[j], f, pb0, pb1);
     }
+  };
+
+  // Two buffers in turn: the next block's loads fly while this one is computed.
+  const int step = MA_WARPS * MA_BLOCK;
+  int tb = t0 + wid * MA_BLOCK;
+  BlockData<FMT, D> bufa, bufb;
+  if (tb < t1) fetch(bufa, tb);
+  while (tb < t1) {
+    if (tb + step < t1) fetch(bufb, tb + step);
+    compute(bufa, tb);
+    tb += step;
+    if (tb >= t1) break;
+    if (tb + step < t1) fetch(bufa, tb + step);
+    compute(bufb, tb);
+    tb += step;
   }
 
   // ---- warps of the CTA, merged in warp order; every column of acc holds the same value ----
