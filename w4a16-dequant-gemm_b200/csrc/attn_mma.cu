@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
-    if (__any_sync(0xffffffffu, bm > m)) {  // the same decision in every lane; rare after the first blocks
+    if (bm > m) {  // the same decision in every lane
       const float corr = __expf(m - bm);  // m = -inf on the first block: 0
       l *= corr;
 #pragma unroll
