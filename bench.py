@@ -492,6 +492,53 @@ def run_reference(args):
     }))
 
 
+def run_profile_case(args):
+    """Small ncu targets: three eager launches of one kernel on a case that holds a few hundred MB."""
+    import torch
+
+    import w4a16_dequant_gemm_b200 as w4
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    case = args.profile_case
+    if case.startswith("attn"):
+        H, S, D, g = 128, 8192, 128, 32
+        G = D // g
+        q = torch.randn(H, D, device=device).to(torch.float16)
+        o = torch.empty(H, D, device=device, dtype=torch.float16)
+        sk = (torch.rand(H, S, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        sv = (torch.rand(H, S, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        if case == "attn_w4":
+            qk = torch.randint(-2**31, 2**31 - 1, (H, S, D // 8), device=device, dtype=torch.int32)
+            qv = torch.randint(-2**31, 2**31 - 1, (H, S, D // 8), device=device, dtype=torch.int32)
+            kv = w4.DeviceKVW4(H, S, D, g, G, 1, qk.data_ptr(), sk.data_ptr(), None, qv.data_ptr(), sv.data_ptr(), None)
+            call = lambda: w4.attention_w4_flash(kv, q.data_ptr(), o.data_ptr())
+        elif case == "attn_f8":
+            bk = torch.randint(0, 0x7E, (H, S, D), device=device, dtype=torch.uint8)
+            bv = torch.randint(0, 0x7E, (H, S, D), device=device, dtype=torch.uint8)
+            f8 = w4.DeviceKVF8(H, S, D, g, G, bk.data_ptr(), sk.data_ptr(), bv.data_ptr(), sv.data_ptr())
+            call = lambda: w4.attention_f8_flash(f8, q.data_ptr(), o.data_ptr())
+        else:
+            k16 = torch.randn(H, S, D, device=device).to(torch.float16)
+            v16 = torch.randn(H, S, D, device=device).to(torch.float16)
+            call = lambda: w4.attention_fp16_flash(q.data_ptr(), k16.data_ptr(), v16.data_ptr(), o.data_ptr(), H, S, D)
+        workload = f"{case}: H={H} S={S} D={D} gs={g}"
+    else:  # gemm_tensor: the headline weights at a prefill-sized M through the tensor kernel
+        N, K, gs, M = N_ROWS, K_COLS, GS, 256
+        qp, s, zp, _ = make_w4_asym(torch, N, K, gs, 1, device)
+        pk = w4.DevicePackedW(N, K, gs, K // gs, 0, qp.data_ptr(), s.data_ptr(), zp.data_ptr())
+        x = torch.randn(M, K, device=device).to(torch.float16)
+        c = torch.empty(M, N, device=device, dtype=torch.float16)
+        call = lambda: w4.gemm(pk, x.data_ptr(), c.data_ptr(), M)
+        workload = f"gemm_tensor: W4 asym gs={gs} N={N} K={K} M={M}"
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    if w4.device_status() != 0:
+        raise SystemExit("bench: device status non-zero")
+    print(json.dumps({"profile": True, "launches": w4.launch_count(), "workload": workload}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -501,7 +548,12 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="run warmup + steps eager launches of the headline GEMM and exit (ncu target)")
+    ap.add_argument("--profile-case", default=None, choices=["attn_w4", "attn_f8", "attn_fp16", "gemm_tensor"],
+                    help="run three eager launches of one secondary kernel on a small case and exit (ncu target)")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args)
+        return
     if args.steps is None:
         args.steps = 20000 if args.impl == "mine" else 50
     if args.warmup is None:
