@@ -7,18 +7,22 @@
 // dequantised W tile is the A operand) by up to 256 activation rows (the UMMA N
 // dimension; x is the B operand) and walks K in chunks of 64:
 //
-//   warp 4  (producer)  TMA: the chunk's packed codes (128 rows x 32 B) and the
+//   warp 8  (producer)  TMA: the chunk's packed codes (128 rows x 32 B) and the
 //                       chunk of x (Mpad rows x 128 B, 128-byte swizzle, rows past
 //                       M zero-filled) into a ring of stages;
-//   warps 0-3 (decode)  thread r decodes row r of the chunk (8 words -> 64 halves,
-//                       the same register decoders as every other kernel, bit-identical
-//                       to dequant_one) and stores them as the canonical K-major
-//                       128-byte-swizzled FP16 operand tile; fence.proxy.async;
-//   warp 5  (MMA)       one thread issues 4 x tcgen05.mma.kind::f16 (M=128, N=Mpad,
+//   warps 0-7 (decode)  thread t decodes half (t >> 7) of row (t & 127) of the chunk
+//                       (4 words -> 32 halves, the same register decoders as every
+//                       other kernel, bit-identical to dequant_one) and stores them
+//                       into the canonical K-major 128-byte-swizzled FP16 operand
+//                       tile; fence.proxy.async. The group's scale / zero point are
+//                       fetched one chunk ahead, outside the wait for the codes;
+//   warp 9  (MMA)       one thread issues 4 x tcgen05.mma.kind::f16 (M=128, N=Mpad,
 //                       K=16) per chunk, accumulating FP32 in TMEM, and
 //                       tcgen05.commit's the stage back to the producer;
-//   warps 0-3 (epilogue) tcgen05.ld the accumulator (lane = weight row), convert to
-//                       FP16 and store c[m*N + n] (a warp writes 32 consecutive n).
+//   warps 0-7 (epilogue) tcgen05.ld the accumulator (lane = weight row; warps w and
+//                       w + 4 share a lane quarter and take alternate column blocks),
+//                       convert to FP16 and store c[m*N + n] (a warp writes 32
+//                       consecutive n).
 //
 // Shapes served: K % 32 == 0 (16-byte row pitch of q and x), 16-byte aligned q / x,
 // any N, any M (grid.y tiles M by 256), any group size the format allows. The K
@@ -36,7 +40,8 @@ constexpr int TK_ROWS = 128;   // weight rows per CTA = UMMA M
 constexpr int TK_KC = 64;      // k per chunk = one 128-byte swizzle row of FP16
 constexpr int TK_A_BYTES = TK_ROWS * 128;
 constexpr int TK_Q_BYTES = TK_ROWS * (TK_KC / 2);
-constexpr int TK_THREADS = 192;
+constexpr int TK_DECODERS = 8;                       // decode warps: two per row quarter, half a chunk each
+constexpr int TK_THREADS = 32 * (TK_DECODERS + 2);  // + TMA producer + MMA issuer
 constexpr int TK_MAX_STAGES = 6;
 
 struct TensorParams {
@@ -46,6 +51,7 @@ struct TensorParams {
   __half* c;
   __half* w_out;
   int N, K, M, gs, G;
+  int gshift;  // log2(gs) when gs is a power of two >= 32, else -1
   int mpad;    // UMMA N: activation rows per CTA rounded up to 16
   int mtile;   // activation rows per CTA (<= 256)
   int stages;
@@ -126,7 +132,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(load_full(s), 1);
-      mbar_init(a_ready(s), 4);
+      mbar_init(a_ready(s), TK_DECODERS);
       mbar_init(stage_free(s), 1);
     }
     mbar_init(acc_ready, 1);
@@ -137,7 +143,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
   // TMEM: power-of-two column count >= 32 covering the Mpad accumulator columns
   uint32_t ncols = 32;
   while (ncols < (uint32_t)a.mpad) ncols <<= 1;
-  if (wid == 5) {
+  if (wid == TK_DECODERS + 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
                  "r"(ncols)
                  : "memory");
@@ -149,7 +155,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
   uint32_t tmem_acc;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_acc) : "r"(tmem_slot) : "memory");
 
-  if (wid == 4) {
+  if (wid == TK_DECODERS) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
       int s = 0;
@@ -165,7 +171,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
         }
       }
     }
-  } else if (wid == 5) {
+  } else if (wid == TK_DECODERS + 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       // instruction descriptor: D = F32, A = B = F16, both K-major, N = Mpad, M = 128
@@ -192,34 +198,62 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
       if (ok) umma_commit(acc_ready);
     }
   } else {
-    // ------------------------- decode warps 0..3 -------------------------
-    const int r = tid;  // row of the tile == TMEM lane
+    // ------------------------- decode warps 0..7 -------------------------
+    // Thread t decodes half `hf` (32 k = 4 packed words) of row r of every chunk.
+    const int r = tid & (TK_ROWS - 1);  // row of the tile == TMEM lane
+    const int hf = tid >> 7;
     const int n = min(n0 + r, a.N - 1);
     const W4Consts kc4 = w4_consts();
     const int wG = words(a.G);
+    // One group per 32 k when the group size is a power of two >= 32 (and for MXFP4's blocks):
+    // its constants are fetched one chunk ahead, outside the wait for the codes.
+    const int gshift = FMT == 2 ? 5 : a.gshift;
+    const bool one_group = gshift >= 5;
+    auto group_of = [&](int kc) { return min((kc * TK_KC + 32 * hf) >> gshift, a.G - 1); };
+    auto fetch_w4 = [&](int grp) {
+      const __half sc = ((const __half*)a.scales)[(size_t)n * a.G + grp];
+      const uint32_t z = FMT == 0 ? 8u : ((a.zeros[(size_t)n * wG + (grp >> 3)] >> (4 * (grp & 7))) & 0xFu);
+      return w4_group(sc, z);
+    };
+    W4Group gnext = w4_group(__ushort_as_half((unsigned short)0), 8u);
+    uint32_t enext = 0;
+    if (one_group) {
+      if (FMT == 2)
+        enext = ((const uint8_t*)a.scales)[(size_t)n * a.G + group_of(0)];
+      else
+        gnext = fetch_w4(group_of(0));
+    }
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
     for (int kc = 0; kc < nchunks; ++kc) {
+      const W4Group gcur = gnext;
+      const uint32_t ecur = enext;
+      if (one_group && kc + 1 < nchunks) {
+        if (FMT == 2)
+          enext = ((const uint8_t*)a.scales)[(size_t)n * a.G + group_of(kc + 1)];
+        else
+          gnext = fetch_w4(group_of(kc + 1));
+      }
       if (!mbar_wait(load_full(s), ph, a.status, ST_TENSOR_TIMEOUT)) {
         ok = false;
         break;
       }
-      const uint4 c0 = lds128(q_tile(s) + (uint32_t)r * 32u), c1 = lds128(q_tile(s) + (uint32_t)r * 32u + 16u);
-      const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      const uint4 c0 = lds128(q_tile(s) + (uint32_t)r * 32u + (uint32_t)hf * 16u);
+      const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
       const uint32_t arow = a_tile(s) + (uint32_t)r * 128u;
+      const MxBlock mcur = mx_block(ecur);
 #pragma unroll
-      for (int w = 0; w < 8; ++w) {
+      for (int j = 0; j < 4; ++j) {
+        const int w = 4 * hf + j;
         const int k0 = kc * TK_KC + 8 * w;
         __half2 o[4];
         if (FMT == 2) {
-          const int blk = min(k0 >> 5, a.G - 1);
-          dq_mx_word(cw[w], mx_block(((const uint8_t*)a.scales)[(size_t)n * a.G + blk]), o);
+          dq_mx_word(cw[j], mcur, o);
+        } else if (one_group) {
+          dq_w4_word(cw[j], gcur, kc4, o);
         } else {
-          const int grp = min(k0 / a.gs, a.G - 1);
-          const __half sc = ((const __half*)a.scales)[(size_t)n * a.G + grp];
-          const uint32_t z = FMT == 0 ? 8u : ((a.zeros[(size_t)n * wG + (grp >> 3)] >> (4 * (grp & 7))) & 0xFu);
-          dq_w4_word(cw[w], w4_group(sc, z), kc4, o);
+          dq_w4_word(cw[j], fetch_w4(min(k0 / a.gs, a.G - 1)), kc4, o);
         }
         const uint4 v = unpair(o);
         sts128(arow + (((uint32_t)w ^ ((uint32_t)r & 7u)) << 4), v);
@@ -237,8 +271,9 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
     // ------------------------------ epilogue ------------------------------
     if (ok && mbar_wait(acc_ready, 0u, a.status, ST_TENSOR_TIMEOUT)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t lane_base = (uint32_t)(wid * 32) << 16;
-      for (int cb = 0; cb < a.mpad; cb += 16) {
+      // warps w and w + 4 own the same TMEM lane quarter and take alternate 16-column blocks
+      const uint32_t lane_base = (uint32_t)((wid & 3) * 32) << 16;
+      for (int cb = 16 * hf; cb < a.mpad; cb += 32) {
         uint32_t v[16];
         tmem_ld16(tmem_acc + lane_base + (uint32_t)cb, v);
         if (n0 + r < a.N) {
@@ -254,7 +289,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (wid == 5) {
+  if (wid == TK_DECODERS + 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(ncols) : "memory");
   }
 }
@@ -311,6 +346,9 @@ cudaError_t tensor_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   tp.K = K;
   tp.M = M;
   tp.gs = gs;
+  tp.gshift = -1;
+  for (int b = 5; b < 31; ++b)
+    if (gs == (1 << b)) tp.gshift = b;
   tp.G = G;
   tp.mtile = M < 256 ? M : 256;
   tp.mpad = (tp.mtile + 15) / 16 * 16;
