@@ -346,13 +346,18 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
-    if (bm > m) {  // the same decision in every lane
+    // A new running maximum (the same decision in every lane; rare after the first blocks).
+    // Written as a loop so that it stays a branch. Only columns 0 of the accumulators are
+    // ever read (every column holds the same sums), so only those are rescaled.
+#pragma unroll 1
+    while (bm > m) {
       const float corr = __expf(m - bm);  // m = -inf on the first block: 0
       l *= corr;
 #pragma unroll
-      for (int j = 0; j < NT; ++j)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[j][i] *= corr;
+      for (int j = 0; j < NT; ++j) {
+        acc[j][0] *= corr;
+        acc[j][2] *= corr;
+      }
       m = bm;
     }
     // weights as FP16 (the MMA's input type); the denominator adds the same rounded values
