@@ -150,3 +150,54 @@ def test_baseline_c4_shape(oracle, fmt):
     sync_ok()
     ref = oracle.attention_reference(q, kd, vd, H, S, D, threads=8)
     assert cases.rel_l2(cases.f16(bits(out)), ref) <= TOL
+
+
+# Every (head size, group size) the tensor-pipe kernel serves, at ragged lengths that leave partial
+# 16-position blocks and partial 64-position slices; W4 symmetric / asymmetric and FP8, with hooks.
+MMA_MATRIX = [(D, gs, S) for D in (64, 128) for gs in (32, 64, 128) if gs <= D for S in (17, 333)] + \
+             [(128, 32, 2049), (64, 32, 1280)]
+
+
+@pytest.mark.parametrize("fmt", ["w4sym", "w4asym", "f8"])
+@pytest.mark.parametrize("D,gs,S", MMA_MATRIX)
+def test_tensor_pipe_matrix(oracle, fmt, D, gs, S):
+    H = 3
+    seed = 0x3A7 + 131 * D + 17 * gs + S
+    kf, vf = oracle.normal_f64(H * S * D, seed), oracle.normal_f64(H * S * D, seed + 1)
+    q = oracle.normal_f16(H * D, seed + 2)
+    q_d = dev(q)
+    out, k_out, v_out = empty_f16(H * D), empty_f16(H * S * D), empty_f16(H * S * D)
+    if fmt == "f8":
+        c = oracle.quantize_cache_f8(kf, vf, H, S, D, gs)
+        kd, vd = oracle.dequant_cache_f8(c, "k"), oracle.dequant_cache_f8(c, "v")
+        kv = KvF8(c)
+        call = lambda o, ko=None, vo=None: w4.attention_f8_flash(kv.desc, ptr(q_d), ptr(o), None, ko, vo)
+    else:
+        c = oracle.quantize_cache_w4(kf, vf, H, S, D, gs, fmt == "w4sym")
+        kd, vd = oracle.dequant_cache_w4(c, "k"), oracle.dequant_cache_w4(c, "v")
+        kv = KvW4(c)
+        call = lambda o, ko=None, vo=None: w4.attention_w4_flash(kv.desc, ptr(q_d), ptr(o), None, ko, vo)
+    call(out, ptr(k_out), ptr(v_out))
+    sync_ok()
+    assert np.array_equal(bits(k_out), kd) and np.array_equal(bits(v_out), vd)  # hooks: bitwise
+    ref = oracle.attention_reference(q, kd, vd, H, S, D)
+    assert cases.rel_l2(cases.f16(bits(out)), ref) <= TOL
+    out2 = empty_f16(H * D)
+    call(out2)
+    sync_ok()
+    assert np.array_equal(bits(out), bits(out2))  # with and without hooks: the same bits
+    # the FP16 entry over the dequantised cache
+    out3, kd_d, vd_d = empty_f16(H * D), dev(kd), dev(vd)
+    w4.attention_fp16_flash(ptr(q_d), ptr(kd_d), ptr(vd_d), ptr(out3), H, S, D)
+    sync_ok()
+    assert cases.rel_l2(cases.f16(bits(out3)), ref) <= TOL
+    if fmt != "f8":
+        # a paged copy with a page size that is no multiple of the kernel's 16-position block
+        page = 24
+        lp = (S + page - 1) // page
+        bt = np.random.default_rng(seed).permutation(lp).astype(np.int32)
+        pool = oracle.paged_from_contiguous(c, page, bt)
+        paged, bt_d, out_p = KvW4(pool), dev(bt), empty_f16(H * D)
+        w4.attention_w4_flash_paged(paged.desc, ptr(bt_d), page, lp, ptr(q_d), ptr(out_p))
+        sync_ok()
+        assert np.array_equal(bits(out_p), bits(out))
