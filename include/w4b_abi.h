@@ -118,8 +118,9 @@ int w4b_gemm_mx(const w4b_packed_mx* p, const void* x, void* c, int M, int path,
                 void* w_out);
 
 /* The same GEMM through HOST activation / output buffers: copies x_host to the
- * device, runs w4b_gemm_w4 (weights stay resident on the device), copies the
- * result into c_host and waits for it. This is the call an application that
+ * device, runs w4b_gemm_w4 (weights stay resident on the device) and waits until
+ * the result is in c_host. A page-locked c_host (cudaHostAlloc / cudaHostRegister)
+ * is written by the kernel itself; pageable memory is filled by a copy. This is the call an application that
  * keeps activations on the host makes; the reference has no such entry (its
  * tests do the two cudaMemcpy themselves, tests/test_gpu.cu:109-113,177-181). */
 int w4b_gemm_w4_hostio(const w4b_packed_w4* p, const void* x_host, void* c_host, int M, int path,

@@ -201,5 +201,8 @@ def test_hostio_entry(oracle):
     c_dev, _ = run_entry(w4.gemm, wts.desc, x_d, M, N, K, False)
     xh = torch.from_numpy(x.view(np.int16).copy()).pin_memory()
     ch = torch.empty(M * N, dtype=torch.int16).pin_memory()
-    w4.gemm_hostio(wts.desc, xh.data_ptr(), ch.data_ptr(), M)
+    w4.gemm_hostio(wts.desc, xh.data_ptr(), ch.data_ptr(), M)  # page-locked: the kernel writes c_host itself
     assert np.array_equal(ch.numpy().view(np.uint16), c_dev)
+    xp, cp = x.copy(), np.zeros(M * N, np.uint16)  # pageable: staged through device memory
+    w4.gemm_hostio(wts.desc, xp.ctypes.data, cp.ctypes.data, M)
+    assert np.array_equal(cp, c_dev)

@@ -258,13 +258,27 @@ int w4b_gemm_w4_hostio(const w4b_packed_w4* p, const void* x_host, void* c_host,
   if (int rc = get_ctx(&ctx)) return rc;
   const size_t xb = (size_t)M * p->K * sizeof(__half), cb = (size_t)M * p->N * sizeof(__half);
   CUDA_TRY(ctx->io_x.reserve(xb, false), "hostio x staging");
-  CUDA_TRY(ctx->io_c.reserve(cb, false), "hostio c staging");
+  // A page-locked output buffer is written by the kernel itself (every CTA stores its slice of c
+  // straight over PCIe); pageable memory goes through a device staging buffer and a copy.
+  void* c_dev = nullptr;
+  {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, c_host) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer)
+      c_dev = at.devicePointer;
+    else
+      (void)cudaGetLastError();
+  }
+  const bool direct = c_dev != nullptr;
+  if (!direct) {
+    CUDA_TRY(ctx->io_c.reserve(cb, false), "hostio c staging");
+    c_dev = ctx->io_c.ptr;
+  }
   cudaStream_t st = (cudaStream_t)stream;
   CUDA_TRY(cudaMemcpyAsync(ctx->io_x.ptr, x_host, xb, cudaMemcpyHostToDevice, st), "hostio h2d");
-  if (int rc = run_gemm(p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, ctx->io_x.ptr,
-                        ctx->io_c.ptr, M, entry, st, nullptr, "gemm kernel"))
+  if (int rc = run_gemm(p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, ctx->io_x.ptr, c_dev,
+                        M, entry, st, nullptr, "gemm kernel"))
     return rc;
-  CUDA_TRY(cudaMemcpyAsync(c_host, ctx->io_c.ptr, cb, cudaMemcpyDeviceToHost, st), "hostio d2h");
+  if (!direct) CUDA_TRY(cudaMemcpyAsync(c_host, c_dev, cb, cudaMemcpyDeviceToHost, st), "hostio d2h");
   CUDA_TRY(cudaStreamSynchronize(st), "hostio sync");
   return W4B_OK;
 }
