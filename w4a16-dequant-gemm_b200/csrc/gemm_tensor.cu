@@ -10,12 +10,13 @@
 //   warp 8  (producer)  TMA: the chunk's packed codes (128 rows x 32 B) and the
 //                       chunk of x (Mpad rows x 128 B, 128-byte swizzle, rows past
 //                       M zero-filled) into a ring of stages;
-//   warps 0-7 (decode)  thread t decodes half (t >> 7) of row (t & 127) of the chunk
-//                       (4 words -> 32 halves, the same register decoders as every
-//                       other kernel, bit-identical to dequant_one) and stores them
-//                       into the canonical K-major 128-byte-swizzled FP16 operand
-//                       tile; fence.proxy.async. The group's scale / zero point are
-//                       fetched one chunk ahead, outside the wait for the codes;
+//   warps 0-7 (decode)  two groups of four warps take alternate chunks; thread t decodes row
+//                       (t & 127) of its group's chunk (8 words -> 64 halves, the same
+//                       register decoders as every other kernel, bit-identical to
+//                       dequant_one) and stores them into the canonical K-major
+//                       128-byte-swizzled FP16 operand tile; fence.proxy.async. The
+//                       groups' scales / zero points are fetched one chunk ahead,
+//                       outside the wait for the codes;
 //   warp 9  (MMA)       one thread issues 4 x tcgen05.mma.kind::f16 (M=128, N=Mpad,
 //                       K=16) per chunk, accumulating FP32 in TMEM, and
 //                       tcgen05.commit's the stage back to the producer;
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(load_full(s), 1);
-      mbar_init(a_ready(s), TK_DECODERS);
+      mbar_init(a_ready(s), TK_DECODERS / 2);  // the four warps of the group that decodes the chunk
       mbar_init(stage_free(s), 1);
     }
     mbar_init(acc_ready, 1);
@@ -199,61 +200,61 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
     }
   } else {
     // ------------------------- decode warps 0..7 -------------------------
-    // Thread t decodes half `hf` (32 k = 4 packed words) of row r of every chunk.
+    // Two groups of four warps take alternate chunks (group = tid >> 7), so one group's waits,
+    // fences and arrivals overlap the other group's decoding. Thread t decodes row r = t & 127
+    // of its group's chunks: 8 packed words -> 64 halves.
     const int r = tid & (TK_ROWS - 1);  // row of the tile == TMEM lane
     const int hf = tid >> 7;
     const int n = min(n0 + r, a.N - 1);
     const W4Consts kc4 = w4_consts();
     const int wG = words(a.G);
-    // One group per 32 k when the group size is a power of two >= 32 (and for MXFP4's blocks):
-    // its constants are fetched one chunk ahead, outside the wait for the codes.
+    // Group sizes that are powers of two >= 32 (and MXFP4's blocks) have one group per 32 k:
+    // the two groups of a chunk are fetched one chunk ahead, outside the wait for the codes.
     const int gshift = FMT == 2 ? 5 : a.gshift;
-    const bool one_group = gshift >= 5;
-    auto group_of = [&](int kc) { return min((kc * TK_KC + 32 * hf) >> gshift, a.G - 1); };
+    const bool pow2 = gshift >= 5;
+    auto group_of = [&](int kc, int h) { return min((kc * TK_KC + 32 * h) >> gshift, a.G - 1); };
     auto fetch_w4 = [&](int grp) {
       const __half sc = ((const __half*)a.scales)[(size_t)n * a.G + grp];
       const uint32_t z = FMT == 0 ? 8u : ((a.zeros[(size_t)n * wG + (grp >> 3)] >> (4 * (grp & 7))) & 0xFu);
       return w4_group(sc, z);
     };
-    W4Group gnext = w4_group(__ushort_as_half((unsigned short)0), 8u);
-    uint32_t enext = 0;
-    if (one_group) {
-      if (FMT == 2)
-        enext = ((const uint8_t*)a.scales)[(size_t)n * a.G + group_of(0)];
-      else
-        gnext = fetch_w4(group_of(0));
-    }
-    int s = 0;
-    uint32_t ph = 0;
-    bool ok = true;
-    for (int kc = 0; kc < nchunks; ++kc) {
-      const W4Group gcur = gnext;
-      const uint32_t ecur = enext;
-      if (one_group && kc + 1 < nchunks) {
+    W4Group gnext[2] = {w4_group(__ushort_as_half((unsigned short)0), 8u), w4_group(__ushort_as_half((unsigned short)0), 8u)};
+    uint32_t enext[2] = {0, 0};
+    auto prefetch = [&](int kc) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
         if (FMT == 2)
-          enext = ((const uint8_t*)a.scales)[(size_t)n * a.G + group_of(kc + 1)];
+          enext[h] = ((const uint8_t*)a.scales)[(size_t)n * a.G + group_of(kc, h)];
         else
-          gnext = fetch_w4(group_of(kc + 1));
+          gnext[h] = fetch_w4(group_of(kc, h));
       }
+    };
+    if (pow2 && hf < nchunks) prefetch(hf);
+    int s = hf % stages;
+    uint32_t ph = (uint32_t)(hf / stages) & 1u;
+    bool ok = true;
+    for (int kc = hf; kc < nchunks; kc += 2) {
+      const W4Group gcur[2] = {gnext[0], gnext[1]};
+      const uint32_t ecur[2] = {enext[0], enext[1]};
+      if (pow2 && kc + 2 < nchunks) prefetch(kc + 2);
       if (!mbar_wait(load_full(s), ph, a.status, ST_TENSOR_TIMEOUT)) {
         ok = false;
         break;
       }
-      const uint4 c0 = lds128(q_tile(s) + (uint32_t)r * 32u + (uint32_t)hf * 16u);
-      const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
+      const uint4 c0 = lds128(q_tile(s) + (uint32_t)r * 32u), c1 = lds128(q_tile(s) + (uint32_t)r * 32u + 16u);
+      const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
       const uint32_t arow = a_tile(s) + (uint32_t)r * 128u;
-      const MxBlock mcur = mx_block(ecur);
+      const MxBlock mcur[2] = {mx_block(ecur[0]), mx_block(ecur[1])};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int w = 4 * hf + j;
+      for (int w = 0; w < 8; ++w) {
         const int k0 = kc * TK_KC + 8 * w;
         __half2 o[4];
         if (FMT == 2) {
-          dq_mx_word(cw[j], mcur, o);
-        } else if (one_group) {
-          dq_w4_word(cw[j], gcur, kc4, o);
+          dq_mx_word(cw[w], mcur[w >> 2], o);
+        } else if (pow2) {
+          dq_w4_word(cw[w], gcur[w >> 2], kc4, o);
         } else {
-          dq_w4_word(cw[j], fetch_w4(min(k0 / a.gs, a.G - 1)), kc4, o);
+          dq_w4_word(cw[w], fetch_w4(min(k0 / a.gs, a.G - 1)), kc4, o);
         }
         const uint4 v = unpair(o);
         sts128(arow + (((uint32_t)w ^ ((uint32_t)r & 7u)) << 4), v);
@@ -263,8 +264,9 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor core reads
       __syncwarp();
       if (lane == 0) mbar_arrive(a_ready(s));
-      if (++s == stages) {
-        s = 0;
+      s += 2;
+      while (s >= stages) {  // the ring is walked two stages at a time
+        s -= stages;
         ph ^= 1u;
       }
     }
