@@ -7,21 +7,21 @@
 // dequantised W tile is the A operand) by up to 256 activation rows (the UMMA N
 // dimension; x is the B operand) and walks K in chunks of 64:
 //
-//   warp 8  (producer)  TMA: the chunk's packed codes (128 rows x 32 B) and the
+//   warp 16 (producer)  TMA: the chunk's packed codes (128 rows x 32 B) and the
 //                       chunk of x (Mpad rows x 128 B, 128-byte swizzle, rows past
 //                       M zero-filled) into a ring of stages;
-//   warps 0-7 (decode)  two groups of four warps take alternate chunks; thread t decodes row
+//   warps 0-15 (decode) four groups of four warps take chunks in turn; thread t decodes row
 //                       (t & 127) of its group's chunk (8 words -> 64 halves, the same
 //                       register decoders as every other kernel, bit-identical to
 //                       dequant_one) and stores them into the canonical K-major
 //                       128-byte-swizzled FP16 operand tile; fence.proxy.async. The
 //                       groups' scales / zero points are fetched one chunk ahead,
 //                       outside the wait for the codes;
-//   warp 9  (MMA)       one thread issues 4 x tcgen05.mma.kind::f16 (M=128, N=Mpad,
+//   warp 17 (MMA)       one thread issues 4 x tcgen05.mma.kind::f16 (M=128, N=Mpad,
 //                       K=16) per chunk, accumulating FP32 in TMEM, and
 //                       tcgen05.commit's the stage back to the producer;
-//   warps 0-7 (epilogue) tcgen05.ld the accumulator (lane = weight row; warps w and
-//                       w + 4 share a lane quarter and take alternate column blocks),
+//   warps 0-15 (epilogue) tcgen05.ld the accumulator (lane = weight row; warps w, w + 4, ...
+//                       share a lane quarter and take alternate column blocks),
 //                       convert to FP16 and store c[m*N + n] (a warp writes 32
 //                       consecutive n).
 //
@@ -41,7 +41,8 @@ constexpr int TK_ROWS = 128;   // weight rows per CTA = UMMA M
 constexpr int TK_KC = 64;      // k per chunk = one 128-byte swizzle row of FP16
 constexpr int TK_A_BYTES = TK_ROWS * 128;
 constexpr int TK_Q_BYTES = TK_ROWS * (TK_KC / 2);
-constexpr int TK_DECODERS = 8;                       // decode warps: two per row quarter, half a chunk each
+constexpr int TK_GROUPS = 4;                        // decode groups of four warps; group g takes chunks g, g + 4, ...
+constexpr int TK_DECODERS = 4 * TK_GROUPS;
 constexpr int TK_THREADS = 32 * (TK_DECODERS + 2);  // + TMA producer + MMA issuer
 constexpr int TK_MAX_STAGES = 6;
 
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(load_full(s), 1);
-      mbar_init(a_ready(s), TK_DECODERS / 2);  // the four warps of the group that decodes the chunk
+      mbar_init(a_ready(s), 4);  // the four warps of the group that decodes the chunk
       mbar_init(stage_free(s), 1);
     }
     mbar_init(acc_ready, 1);
@@ -200,8 +201,8 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
     }
   } else {
     // ------------------------- decode warps 0..7 -------------------------
-    // Two groups of four warps take alternate chunks (group = tid >> 7), so one group's waits,
-    // fences and arrivals overlap the other group's decoding. Thread t decodes row r = t & 127
+    // TK_GROUPS groups of four warps take chunks in turn (group = tid >> 7), so one group's waits,
+    // fences and arrivals overlap the other groups' decoding. Thread t decodes row r = t & 127
     // of its group's chunks: 8 packed words -> 64 halves.
     const int r = tid & (TK_ROWS - 1);  // row of the tile == TMEM lane
     const int hf = tid >> 7;
@@ -233,10 +234,10 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
     int s = hf % stages;
     uint32_t ph = (uint32_t)(hf / stages) & 1u;
     bool ok = true;
-    for (int kc = hf; kc < nchunks; kc += 2) {
+    for (int kc = hf; kc < nchunks; kc += TK_GROUPS) {
       const W4Group gcur[2] = {gnext[0], gnext[1]};
       const uint32_t ecur[2] = {enext[0], enext[1]};
-      if (pow2 && kc + 2 < nchunks) prefetch(kc + 2);
+      if (pow2 && kc + TK_GROUPS < nchunks) prefetch(kc + TK_GROUPS);
       if (!mbar_wait(load_full(s), ph, a.status, ST_TENSOR_TIMEOUT)) {
         ok = false;
         break;
@@ -264,8 +265,8 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor core reads
       __syncwarp();
       if (lane == 0) mbar_arrive(a_ready(s));
-      s += 2;
-      while (s >= stages) {  // the ring is walked two stages at a time
+      s += TK_GROUPS;
+      while (s >= stages) {  // the ring is walked TK_GROUPS stages at a time
         s -= stages;
         ph ^= 1u;
       }
@@ -273,9 +274,9 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
     // ------------------------------ epilogue ------------------------------
     if (ok && mbar_wait(acc_ready, 0u, a.status, ST_TENSOR_TIMEOUT)) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // warps w and w + 4 own the same TMEM lane quarter and take alternate 16-column blocks
+      // warps w, w + 4, ... own the same TMEM lane quarter and take alternate 16-column blocks
       const uint32_t lane_base = (uint32_t)((wid & 3) * 32) << 16;
-      for (int cb = 16 * hf; cb < a.mpad; cb += 32) {
+      for (int cb = 16 * hf; cb < a.mpad; cb += 16 * TK_GROUPS) {
         uint32_t v[16];
         tmem_ld16(tmem_acc + lane_base + (uint32_t)cb, v);
         if (n0 + r < a.N) {
