@@ -54,7 +54,7 @@ def measured_peak():
 
 
 # ---------------------------------------------------------------------------
-# clocks sampler (nvidia-smi, read-only)
+# clocks sampler (NVML or nvidia-smi, read-only)
 # ---------------------------------------------------------------------------
 class Clocks:
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -62,9 +62,25 @@ class Clocks:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.rows, self.proc, self.index = [], None, index
+        self.rows, self.proc, self.index, self.nvml = [], None, index, None
 
     def start(self):
+        """Samples through NVML in a thread (first choice: no process start-up), else through nvidia-smi."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                import torch
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+                h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nvml = (pynvml, h)
+            self._stop = False
+            threading.Thread(target=self._poll, daemon=True).start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
@@ -72,15 +88,39 @@ class Clocks:
             self.proc = None
             return
         threading.Thread(target=self._read, daemon=True).start()
+        t0 = time.time()
+        while not self.rows and time.time() - t0 < 5.0:  # nvidia-smi needs a moment before its first line
+            time.sleep(0.02)
+
+    def _poll(self):
+        nv, h = self.nvml
+        act = lambda on: "Active" if on else "Not Active"
+        while not self._stop:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                # same columns as the nvidia-smi query: index, sm, max, power, reasons.active, hw, hw_thermal, sw_thermal, sw_power
+                self.rows.append((time.time(), [str(self.index), str(sm), str(mx), "", hex(r), act(r & 0x8), act(r & 0x40),
+                                                act(r & 0x20), act(r & 0x4)]))
+            except Exception:
+                pass
+            time.sleep(0.01)
 
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
     def stop(self, t0, t1):
-        if self.proc is None:
+        if self.nvml is not None:
+            self._stop = True
+        elif self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+        else:
+            self.proc.terminate()
         inside = [r for t, r in self.rows if t0 <= t <= t1]
         window = "timed region"
         if not inside:  # region shorter than the sampling period: fall back to the loaded part of the run
@@ -154,23 +194,51 @@ def run_mine(args):
     g = torch.Generator(device=device).manual_seed(7)
     x = torch.randn(M, K, generator=g, device=device, dtype=torch.float32).to(torch.float16)
     c = torch.empty(M, N, device=device, dtype=torch.float16)
-    gathered = torch.empty(world, M, N, device=device, dtype=torch.float16) if world > 1 else None
     stream = torch.cuda.current_stream().cuda_stream
+    pg = None
+    if world > 1:
+        # the exchange step: every rank's output slice goes to every rank over NVLink peer stores
+        def exchange(handle):
+            out = [None] * world
+            dist.all_gather_object(out, handle)
+            return out
+        pg = w4.peer.PeerGather(M * N * 2, rank, world, exchange)
 
-    def step(i):
-        w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, stream)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), c.view(-1))
+    def step(i, st=None):
+        st = stream if st is None else st
+        if world == 1:
+            w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, st)
+        else:
+            buf = i % w4.peer.NBUF  # slice buffers in rotation
+            w4.gemm(packs[i % copies][3], x.data_ptr(), pg.slot(buf, rank), M, st)
+            pg.push(buf, st)  # (waits for the peers' previous slices only; pg.wait() completes a sequence)
+
+    class _Arena:  # a window of device memory as a torch tensor of int16
+        def __init__(self, ptr, n):
+            self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<i2", "data": (ptr, False), "version": 2}
 
     # parity at bench size against a plain FP32 product of the dequantised weights
     step(0)
+    if world > 1:
+        pg.wait(stream)
     torch.cuda.synchronize()
+    if world > 1:  # the step wrote this rank's slice into its arena
+        c.view(torch.int16).view(-1).copy_(torch.as_tensor(_Arena(pg.slot(0, rank), M * N), device=device))
     ref = x.float() @ wdeq0.float().t()
     rel = float(((c.float() - ref).norm() / ref.norm()).item())
     status = w4.device_status()
     del wdeq0, ref
     if status != 0 or not rel <= 1e-3:
         raise SystemExit(f"bench: parity check failed (rel L2 {rel:.3e}, device status {status})")
+    if world > 1:
+        # the peer all-gather against NCCL's, byte for byte
+        mine = torch.as_tensor(_Arena(pg.slot(0, 0), world * pg.lay["slot"] // 2), device=device)
+        mine = mine.view(world, pg.lay["slot"] // 2)[:, :M * N].clone()
+        local = mine[rank].contiguous()
+        want = torch.empty(world, M * N, device=device, dtype=torch.float16)  # (NCCL has no int16)
+        dist.all_gather_into_tensor(want.view(-1), local.view(torch.float16))
+        if not torch.equal(mine, want.view(torch.int16)):
+            raise SystemExit("bench: the peer all-gather differs from the NCCL all-gather")
 
     if args.profile:
         # profiling target (run under ncu on one GPU): a few eager launches of the headline GEMM, nothing else
@@ -185,17 +253,27 @@ def run_mine(args):
         clocks.start()
     for i in range(max(args.warmup, 3)):
         step(i)
-    t_settle = time.time()
-    while time.time() - t_settle < 0.5:  # keep the GPU loaded until the clocks have settled
+    # keep the GPU loaded until the clocks have settled: for half a second on one GPU, for a fixed
+    # number of steps when the step holds an exchange (every rank must run the same number of steps)
+    t_settle, rounds = time.time(), 0
+    while (time.time() - t_settle < 0.5) if world == 1 else (rounds < 100):
         for i in range(200):
             step(i)
+        if world > 1:
+            pg.wait(stream)
         torch.cuda.synchronize()
+        rounds += 1
+    if world > 1:  # a peer wait that ran out anywhere ends every rank here, not in a later barrier
+        bad = torch.tensor([w4.device_status()], device=device)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()) != 0:
+            dist.destroy_process_group()
+            raise SystemExit(f"bench: a bounded device wait ran out (status {int(bad.item())})")
 
-    # On one GPU the K steps are captured once in a CUDA graph, so the timed region holds device work
-    # only. With NCCL in the step the steps are launched eagerly: capturing the collectives hung here
-    # (both ranks stalled after capture), so that route is not taken.
+    # The K steps are captured once in a CUDA graph, so the timed region holds device work only. At
+    # N > 1 a step is the GEMM plus the peer all-gather kernel; no NCCL call is in the graph.
     launches_before = w4.launch_count()
-    use_graph = world == 1
+    use_graph = True
     if use_graph:
         side = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
@@ -203,11 +281,17 @@ def run_mine(args):
             sstream = side.cuda_stream
             graph.capture_begin()
             for i in range(args.steps):
-                w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, sstream)
+                step(i, sstream)
+            if world > 1:
+                pg.wait(sstream)  # the graph ends when the last step's slices are here
             graph.capture_end()
         launches_captured = w4.launch_count() - launches_before
+        if world > 1:
+            dist.barrier()
         graph.replay()  # untimed: uploads the graph
         torch.cuda.synchronize()
+        if w4.device_status() != 0:
+            raise SystemExit("bench: a bounded device wait ran out during the untimed replay")
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
@@ -286,9 +370,10 @@ def run_mine(args):
         "config": {"workload": WORKLOAD, "us_per_gemm": round(us_per_step, 3),
                    "algorithmic_bytes_per_gemm": bytes_per_gemm,
                    "l2": f"weights rotate over {copies} copies ({copies * bytes_per_gemm / 1e6:.0f} MB > 126 MB L2)",
-                   "timing": "one CUDA graph of K launches, CUDA events" if use_graph else
-                             "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks",
-                   "parallelism": "single GPU" if world == 1 else f"column-parallel N x{world} + all-gather",
+                   "timing": "one CUDA graph of K launches, CUDA events" if world == 1 else
+                             "one CUDA graph of K steps (GEMM + peer all-gather kernel; a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
+                   "parallelism": "single GPU" if world == 1 else
+                                  f"column-parallel N x{world} + all-gather over NVLink peer stores",
                    "rel_l2_vs_fp32_product": rel},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH,

@@ -173,6 +173,38 @@ int w4b_attn_single_fp16(const void* q, const void* k16, const void* v16, void* 
 int w4b_attn_single_w4(const w4b_kv_w4* p, const void* q, void* out, void* stream, void* k_out,
                        void* v_out);
 
+/* ---- all-gather of the sharded GEMM's output over NVLink peer memory ----- */
+
+/* These six entries have no counterpart in the reference (it is single-GPU). They
+ * are the exchange step of the column-parallel GEMM: one process per GPU, every
+ * rank owns an arena that its peers map through CUDA IPC, and one launch per step
+ * stores this rank's output slice into every peer's arena with plain peer stores
+ * and posts a step flag. Before storing, a step waits (bounded, ~1 s, then the
+ * device status word is set) for the peers' slices of the PREVIOUS step, so ranks
+ * stay within one step of each other; with wait_now != 0 it also waits for the
+ * peers' slices of its own step (a complete all-gather in one launch).
+ * w4b_allgather_wait does that wait on its own: after it, every slice of the last
+ * pushed step is in this rank's arena. Graph-capturable: step numbers come from a
+ * counter in the arena. world <= 8. With wait_now == 0 the caller rotates over
+ * three slice buffers (a slice is then never overwritten while a peer may read
+ * it); with wait_now != 0 two suffice.
+ *
+ * w4b_peer_alloc: cudaMalloc + zero-fill an arena and return its 64-byte IPC handle.
+ * w4b_peer_open / _close: map / unmap a peer's arena from its handle.
+ * w4b_allgather_push: dst[p] = where the slice goes in rank p's arena, flag_dst[p] =
+ *   rank p's 64-bit flag word for this rank (entries [rank] are ignored),
+ *   flags_local = this rank's flag words (world x uint64), counters = world zero-
+ *   initialised uint64 in this rank's arena. dst, flag_dst are HOST arrays of device
+ *   pointers. */
+int w4b_peer_alloc(size_t bytes, void** ptr, void* handle64);
+int w4b_peer_open(const void* handle64, void** ptr);
+int w4b_peer_close(void* ptr);
+int w4b_peer_free(void* ptr);
+int w4b_allgather_push(const void* src, size_t bytes, void* const* dst, void* const* flag_dst,
+                       const void* flags_local, void* counters, int rank, int world, int wait_now,
+                       void* stream);
+int w4b_allgather_wait(const void* flags_local, const void* counters, int rank, int world, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -5,3 +5,4 @@ from . import build  # noqa: F401
 from .capi import *  # noqa: F401,F403
 from . import capi  # noqa: F401
 from . import shard  # noqa: F401
+from . import peer  # noqa: F401

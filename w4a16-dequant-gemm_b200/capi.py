@@ -70,6 +70,12 @@ ABI = {
     "w4b_attn_flash_w4_paged": (_I, [C.POINTER(_KvW4), _P, _I, _I, _P, _P, _P, _P, _P]),
     "w4b_attn_single_fp16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "w4b_attn_single_w4": (_I, [C.POINTER(_KvW4), _P, _P, _P, _P, _P]),
+    "w4b_peer_alloc": (_I, [C.c_size_t, C.POINTER(_P), _P]),
+    "w4b_peer_open": (_I, [_P, C.POINTER(_P)]),
+    "w4b_peer_close": (_I, [_P]),
+    "w4b_peer_free": (_I, [_P]),
+    "w4b_allgather_push": (_I, [_P, C.c_size_t, C.POINTER(_P), C.POINTER(_P), _P, _P, _I, _I, _I, _P]),
+    "w4b_allgather_wait": (_I, [_P, _P, _I, _I, _P]),
 }
 
 
@@ -253,3 +259,41 @@ def device_status() -> int:
 
 def launch_count() -> int:
     return int(lib.w4b_launch_count())
+
+
+# ---- all-gather over peer memory (no reference counterpart) ----------------------------------
+
+def peer_alloc(nbytes: int):
+    """cudaMalloc + zero-fill an arena on the current device; returns (device address, 64-byte IPC handle)."""
+    ptr, handle = _P(), C.create_string_buffer(64)
+    _check(lib.w4b_peer_alloc(nbytes, C.byref(ptr), handle))
+    return ptr.value, handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    """Map a peer's arena from its IPC handle; returns its address in this process."""
+    ptr = _P()
+    _check(lib.w4b_peer_open(C.create_string_buffer(handle, 64), C.byref(ptr)))
+    return ptr.value
+
+
+def peer_close(ptr: int):
+    _check(lib.w4b_peer_close(ptr))
+
+
+def peer_free(ptr: int):
+    _check(lib.w4b_peer_free(ptr))
+
+
+def allgather_push(src, nbytes, dst, flag_dst, flags_local, counters, rank, world, wait_now=True, stream=None):
+    """One all-gather step: push the slice at `src` to every peer's `dst[p]` and post the step flag; wait for
+    the peers' slices of this step (wait_now) or only of the previous one."""
+    arr = _P * world
+    _check(lib.w4b_allgather_push(src, nbytes, arr(*dst), arr(*flag_dst), flags_local, counters, rank, world,
+                                  1 if wait_now else 0, stream))
+
+
+def allgather_wait(flags_local, counters, rank, world, stream=None):
+    """Wait (on the stream) until every peer's slice of the last pushed step has arrived."""
+    _check(lib.w4b_allgather_wait(flags_local, counters, rank, world, stream))
+

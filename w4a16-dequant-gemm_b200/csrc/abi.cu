@@ -470,4 +470,93 @@ int w4b_attn_flash_w4_paged(const w4b_kv_w4* p, const int* bt, int page, int npa
   return run_attn(s, q, out, p->H, p->S, p->D, (cudaStream_t)stream, k_out, v_out, "kv paged flash");
 }
 
+// ---- all-gather over peer memory (no reference counterpart) --------------------------------
+
+int w4b_peer_alloc(size_t bytes, void** ptr, void* handle64) {
+  if (!ptr || !handle64 || bytes == 0) INVALID("peer alloc: null pointer or empty size");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  void* p = nullptr;
+  CUDA_TRY(cudaMalloc(&p, bytes), "peer alloc");
+  CUDA_TRY(cudaMemset(p, 0, bytes), "peer alloc clear");
+  CUDA_TRY(cudaDeviceSynchronize(), "peer alloc clear");
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "peer alloc: cudaIpcGetMemHandle");
+  }
+  memcpy(handle64, &h, sizeof(h));
+  *ptr = p;
+  return W4B_OK;
+}
+
+int w4b_peer_open(const void* handle64, void** ptr) {
+  if (!ptr || !handle64) INVALID("peer open: null pointer");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess), "peer open: cudaIpcOpenMemHandle");
+  return W4B_OK;
+}
+
+int w4b_peer_close(void* ptr) {
+  if (!ptr) INVALID("peer close: null pointer");
+  CUDA_TRY(cudaIpcCloseMemHandle(ptr), "peer close");
+  return W4B_OK;
+}
+
+int w4b_peer_free(void* ptr) {
+  if (!ptr) INVALID("peer free: null pointer");
+  CUDA_TRY(cudaFree(ptr), "peer free");
+  return W4B_OK;
+}
+
+int w4b_allgather_push(const void* src, size_t bytes, void* const* dst, void* const* flag_dst, const void* flags_local,
+                       void* counters, int rank, int world, int wait_now, void* stream) {
+  if (world < 2 || world > kMaxPeers) INVALID("allgather push: world must be 2..%d", kMaxPeers);
+  if (rank < 0 || rank >= world) INVALID("allgather push: rank out of range");
+  if (!src || !dst || !flag_dst || !flags_local || !counters) INVALID("allgather push: null pointer");
+  if (bytes == 0 || bytes % 16 != 0 || ((uintptr_t)src & 15u)) INVALID("allgather push: slice must be 16-byte sized and aligned");
+  if (((uintptr_t)flags_local | (uintptr_t)counters) & 7u) INVALID("allgather push: flags must be 8-byte aligned");
+  PeerPush pp;
+  memset(&pp, 0, sizeof(pp));
+  for (int p = 0; p < world; ++p) {
+    if (p == rank) continue;
+    if (!dst[p] || !flag_dst[p] || ((uintptr_t)dst[p] & 15u) || ((uintptr_t)flag_dst[p] & 7u))
+      INVALID("allgather push: bad destination for peer %d", p);
+    pp.dst[p] = dst[p];
+    pp.flag_dst[p] = flag_dst[p];
+  }
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  pp.src = src;
+  pp.n16 = bytes / 16;
+  pp.flags_local = flags_local;
+  pp.counters = (unsigned long long*)counters;
+  pp.rank = rank;
+  pp.world = world;
+  pp.wait_now = wait_now ? 1 : 0;
+  pp.status = ctx->status;
+  CUDA_TRY(peer_push_launch(pp, (cudaStream_t)stream), "allgather push kernel");
+  g_launches += 1;
+  return W4B_OK;
+}
+
+int w4b_allgather_wait(const void* flags_local, const void* counters, int rank, int world, void* stream) {
+  if (world < 2 || world > kMaxPeers) INVALID("allgather wait: world must be 2..%d", kMaxPeers);
+  if (rank < 0 || rank >= world) INVALID("allgather wait: rank out of range");
+  if (!flags_local || !counters || (((uintptr_t)flags_local | (uintptr_t)counters) & 7u))
+    INVALID("allgather wait: flags must be non-null and 8-byte aligned");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(peer_wait_launch(flags_local, (const unsigned long long*)counters, rank, world, ctx->status,
+                            (cudaStream_t)stream),
+           "allgather wait kernel");
+  g_launches += 1;
+  return W4B_OK;
+}
+
 }  // extern "C"

@@ -24,6 +24,7 @@ enum : int {
   ST_STREAM_PANEL_TIMEOUT = 103,  // stream GEMM: a panel owner never saw the other CTAs' fragments
   ST_TENSOR_TIMEOUT = 201,        // tensor GEMM: a pipeline wait ran out
   ST_FLASH_TIMEOUT = 301,         // flash decode: a pipeline wait ran out
+  ST_PEER_TIMEOUT = 401,          // peer all-gather: a peer's slice never arrived
 };
 
 // --------------------------------------------------------------------------

@@ -87,4 +87,21 @@ bool attn_mma_supported(const AttnSource& src, int D, const void* q, const void*
 cudaError_t attn_mma_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
                             float* ws, __half* k_out, __half* v_out, cudaStream_t stream);
 
+// ---- peer_gather.cu ---------------------------------------------------------
+constexpr int kMaxPeers = 8;
+struct PeerPush {
+  const void* src;                // this rank's slice (in its own arena)
+  size_t n16;                     // its size in 16-byte units
+  void* dst[kMaxPeers];           // where the slice goes in rank p's arena
+  void* flag_dst[kMaxPeers];      // rank p's flag word for this rank
+  const void* flags_local;        // this rank's flag words, one per peer (uint64)
+  unsigned long long* counters;   // steps pushed to each peer, one uint64 per rank (start at zero)
+  int rank, world;
+  int wait_now;                   // also wait for the peers' slices of this step (else: of the previous one only)
+  int* status;
+};
+cudaError_t peer_push_launch(const PeerPush& p, cudaStream_t stream);
+cudaError_t peer_wait_launch(const void* flags_local, const unsigned long long* counters, int rank, int world,
+                             int* status, cudaStream_t stream);
+
 }  // namespace w4b
