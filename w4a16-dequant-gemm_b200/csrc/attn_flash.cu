@@ -285,11 +285,14 @@ cudaError_t launch_fmt(const FlashParams& p, cudaStream_t stream) {
 
 int attn_flash_splits(int H, int S, int sm_count) {
   // About eight waves of CTAs at four resident CTAs per SM (a partial last wave then costs
-  // little). Slices of at least 256 positions (four steps per warp) while that still gives
-  // every SM four CTAs, else of at least FA_MIN_SPLIT.
+  // little), but slices as long as possible - 256 positions (four steps per warp), else 128, else
+  // FA_MIN_SPLIT - as long as that still gives every SM two CTAs.
   long long want = (32LL * sm_count + H - 1) / H;
-  long long cap = (S + 255) / 256;
-  if (cap * H < 4LL * sm_count) cap = (S + FA_MIN_SPLIT - 1) / FA_MIN_SPLIT;
+  long long cap = 1;
+  for (int slice = 256; slice >= FA_MIN_SPLIT; slice >>= 1) {
+    cap = (S + slice - 1) / slice;
+    if (cap * H >= 2LL * sm_count) break;
+  }
   if (want > cap) want = cap;
   if (want > 65535) want = 65535;
   if (want < 1) want = 1;
