@@ -12,13 +12,13 @@
 //    panel-major / chunk-fastest and cut into equal contiguous ranges, one per
 //    persistent CTA (one CTA per SM), so all SMs finish together whatever N and
 //    K are ("stream-K").
-//  * Warp 16 is the producer: per unit it issues the TMA box plus 4..16-byte
+//  * The last warp is the producer: per unit it issues the TMA box plus 4..16-byte
 //    cp.async copies of the unit's scales / zero words into a ring of up to 22
 //    stages; full/empty mbarriers hand stages over, so ~200 KB per SM are in
 //    flight from the first microsecond.
-//  * Warps 0..15 are consumers: warp w owns the 16-row tile (w & 3) of every
-//    fourth unit (phase w >> 2), which keeps four stages under computation at a
-//    time. A lane decodes packed words in registers (w4b_common.cuh: no tables,
+//  * The other 4 x PH warps are consumers (PH = 2 unit phases for W4, 4 for
+//    MXFP4): warp w owns the 16-row tile (w & 3) of every PH-th unit (phase
+//    w >> 2), which keeps PH stages under computation at a time. A lane decodes packed words in registers (w4b_common.cuh: no tables,
 //    no local memory) straight into mma.sync m16n8k16 A fragments; the
 //    activations sit in shared memory, arranged once per CTA in the decoder's
 //    pairing, and are the B fragments; FP32 accumulators stay in registers
@@ -55,13 +55,16 @@ constexpr int SK_STAGE_Q = SK_ROWS * SK_KC / 2;  // 8192 bytes of codes per unit
 constexpr int SK_META_SCALES = SK_ROWS * 16;     // <= 8 FP16 scales or 8 E8M0 bytes per row
 constexpr int SK_META = SK_META_SCALES + SK_ROWS * 4;  // + one zero word per row
 constexpr int SK_TILES = 4;
-constexpr int SK_PHASES = 4;
-constexpr int SK_CONSUMERS = SK_TILES * SK_PHASES;
-constexpr int SK_THREADS = 32 * (SK_CONSUMERS + 1);
+// Unit phases: consumer warp w owns tile (w & 3) of every PH-th unit (phase w >> 2). Measured on B200: the W4
+// decoders run best with 2 phases (8 consumer warps; 4 phases are 6 % slower at the headline shape, 6 phases
+// 12 %), the heavier MXFP4 decode with 4 (2 phases are 30 % slower there).
+constexpr int SK_MAX_PHASES = 4;
+__host__ __device__ constexpr int sk_phases(int fmt) { return fmt == 2 ? 4 : 2; }
+__host__ __device__ constexpr int sk_threads(int fmt) { return 32 * (SK_TILES * sk_phases(fmt) + 1); }
 constexpr int SK_MAX_STAGES = 22;
 constexpr int SK_BURST = 4;  // units the producer issues back to back
 constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 2);  // ring barriers + "parked" + "collected"
-constexpr int SK_RED_BYTES_PER_MT = SK_TILES * (SK_PHASES - 1) * 32 * 16;  // cross-phase exchange
+constexpr int SK_RED_BYTES_PER_MT = SK_TILES * (SK_MAX_PHASES - 1) * 32 * 16;  // cross-phase exchange
 constexpr int SK_COLLECT_BYTES_PER_MT = SK_TILES * 32 * 16;               // other CTAs' fragments, summed
 
 enum : int { F_W4_SYM = 0, F_W4_ASYM = 1, F_MX = 2 };
@@ -241,8 +244,10 @@ constexpr int BAR_TAKEN = 5;    // +tile: phase 0 has read them (phases 1..3 wai
 constexpr int BAR_XFILL = 9;    // all consumer warps: the activations are in shared memory
 
 template <int FMT, int GS, int MT, bool HOOK>
-__global__ void __launch_bounds__(SK_THREADS, 1)
+__global__ void __launch_bounds__(sk_threads(FMT), 1)
     stream_gemm_kernel(const __grid_constant__ CUtensorMap tmap, const StreamParams a) {
+  constexpr int SK_PHASES = sk_phases(FMT);
+  constexpr int SK_CONSUMERS = SK_TILES * SK_PHASES;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
   const int stages = a.stages;
@@ -567,7 +572,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     }
     named_barrier(BAR_HANDED + tile, 32 * SK_PHASES);
 #pragma unroll
-    for (int f = 0; f < SK_PHASES - 1; ++f)  // fixed order: phase 1, 2, 3
+    for (int f = 0; f < SK_PHASES - 1; ++f)  // fixed order: phase 1, 2, ...
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const float4 v = red[(f * MT + mt) * 32 + lane];
@@ -662,7 +667,7 @@ cudaError_t launch_one(const CUtensorMap& tmap, const StreamParams& sp, dim3 gri
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  kern<<<grid, SK_THREADS, smem, stream>>>(tmap, sp);
+  kern<<<grid, sk_threads(FMT), smem, stream>>>(tmap, sp);
   return cudaGetLastError();
 }
 
