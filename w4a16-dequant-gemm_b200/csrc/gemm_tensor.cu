@@ -44,7 +44,7 @@ constexpr int TK_Q_BYTES = TK_ROWS * (TK_KC / 2);
 constexpr int TK_GROUPS = 4;                        // decode groups of four warps; group g takes chunks g, g + 4, ...
 constexpr int TK_DECODERS = 4 * TK_GROUPS;
 constexpr int TK_THREADS = 32 * (TK_DECODERS + 2);  // + TMA producer + MMA issuer
-constexpr int TK_MAX_STAGES = 6;
+constexpr int TK_MAX_STAGES = 8;   // (a multiple of TK_GROUPS, see the launcher)
 
 struct TensorParams {
   const uint32_t* q;
@@ -357,7 +357,13 @@ cudaError_t tensor_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   tp.mpad = (tp.mtile + 15) / 16 * 16;
   const size_t stage_bytes = TK_A_BYTES + (size_t)tp.mpad * 128 + TK_Q_BYTES;
   int stages = (int)((232448 - 1024 - 8 * (3 * TK_MAX_STAGES + 2)) / stage_bytes);
-  tp.stages = stages > TK_MAX_STAGES ? TK_MAX_STAGES : stages;
+  // The ring depth is a multiple of the number of decode groups, so that a stage is always decoded by the
+  // same group: a group then waits for fill n of a stage only after it has consumed fill n - 1 (an mbarrier
+  // phase may be awaited at most one phase ahead - with more groups than stages a group would "pass" a wait
+  // for a fill that has not even started; six groups over four stages faulted that way).
+  stages = stages > TK_MAX_STAGES ? TK_MAX_STAGES : stages;
+  tp.stages = stages / TK_GROUPS * TK_GROUPS;
+  if (tp.stages < TK_GROUPS) return cudaErrorInvalidConfiguration;  // cannot happen: a stage is at most 52 KB
   tp.status = status;
   const size_t smem = 1024 + (size_t)tp.stages * stage_bytes + 8 * (3 * TK_MAX_STAGES + 2);
 
