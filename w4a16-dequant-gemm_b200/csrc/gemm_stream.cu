@@ -758,7 +758,11 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   sp.C = plan.C;
   sp.P = plan.P;
   sp.U = (int)plan.U;
-  sp.stages = plan.stages;
+  // A multiple of the format's phase count: a ring slot is then always consumed by the same phase, so a warp
+  // waits for fill n of a slot only after it has itself consumed fill n - 1 (an mbarrier phase may be awaited
+  // at most one phase ahead). (The plan's shared-memory size covers the unrounded depth.)
+  sp.stages = fmt == F_MX ? plan.stages / sk_phases(F_MX) * sk_phases(F_MX)
+                          : plan.stages / sk_phases(F_W4_SYM) * sk_phases(F_W4_SYM);
   sp.xpitch = plan.xpitch;
   sp.ws = ws;
   sp.counters = counters;
