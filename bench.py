@@ -202,12 +202,28 @@ def run_mine(args):
             out = [None] * world
             dist.all_gather_object(out, handle)
             return out
-        pg = w4.peer.PeerGather(M * N * 2, rank, world, exchange)
+        # If the arenas cannot be set up on some rank (no peer access between the GPUs, IPC refused), every
+        # rank falls back to NCCL's all-gather for the exchange (eager steps; its capture stalled here).
+        try:
+            pg = w4.peer.PeerGather(M * N * 2, rank, world, exchange)
+            ok = 1
+        except Exception as e:  # noqa: BLE001
+            print(f"bench: rank {rank}: peer arenas unavailable ({e}); NCCL all-gather instead", file=sys.stderr)
+            pg, ok = None, 0
+        flag = torch.tensor([ok], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            pg = None
+    peer_mode = pg is not None
+    gathered = torch.empty(world, M, N, device=device, dtype=torch.float16) if (world > 1 and not peer_mode) else None
 
     def step(i, st=None):
         st = stream if st is None else st
         if world == 1:
             w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, st)
+        elif not peer_mode:
+            w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, st)
+            dist.all_gather_into_tensor(gathered.view(-1), c.view(-1))
         else:
             buf = i % w4.peer.NBUF  # slice buffers in rotation
             w4.gemm(packs[i % copies][3], x.data_ptr(), pg.slot(buf, rank), M, st)
@@ -219,10 +235,10 @@ def run_mine(args):
 
     # parity at bench size against a plain FP32 product of the dequantised weights
     step(0)
-    if world > 1:
+    if peer_mode:
         pg.wait(stream)
     torch.cuda.synchronize()
-    if world > 1:  # the step wrote this rank's slice into its arena
+    if peer_mode:  # the step wrote this rank's slice into its arena
         c.view(torch.int16).view(-1).copy_(torch.as_tensor(_Arena(pg.slot(0, rank), M * N), device=device))
     ref = x.float() @ wdeq0.float().t()
     rel = float(((c.float() - ref).norm() / ref.norm()).item())
@@ -230,7 +246,7 @@ def run_mine(args):
     del wdeq0, ref
     if status != 0 or not rel <= 1e-3:
         raise SystemExit(f"bench: parity check failed (rel L2 {rel:.3e}, device status {status})")
-    if world > 1:
+    if peer_mode:
         # the peer all-gather against NCCL's, byte for byte
         mine = torch.as_tensor(_Arena(pg.slot(0, 0), world * pg.lay["slot"] // 2), device=device)
         mine = mine.view(world, pg.lay["slot"] // 2)[:, :M * N].clone()
@@ -259,7 +275,7 @@ def run_mine(args):
     while (time.time() - t_settle < 0.5) if world == 1 else (rounds < 100):
         for i in range(200):
             step(i)
-        if world > 1:
+        if peer_mode:
             pg.wait(stream)
         torch.cuda.synchronize()
         rounds += 1
@@ -273,16 +289,16 @@ def run_mine(args):
     # The K steps are captured once in a CUDA graph, so the timed region holds device work only. At
     # N > 1 a step is the GEMM plus the peer all-gather kernel; no NCCL call is in the graph.
     launches_before = w4.launch_count()
-    use_graph = True
+    use_graph = world == 1 or peer_mode
     if use_graph:
         side = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
             sstream = side.cuda_stream
-            graph.capture_begin()
+            graph.capture_begin(capture_error_mode="thread_local")  # (NCCL's watchdog thread queries events meanwhile)
             for i in range(args.steps):
                 step(i, sstream)
-            if world > 1:
+            if peer_mode:
                 pg.wait(sstream)  # the graph ends when the last step's slices are here
             graph.capture_end()
         launches_captured = w4.launch_count() - launches_before
@@ -371,9 +387,11 @@ def run_mine(args):
                    "algorithmic_bytes_per_gemm": bytes_per_gemm,
                    "l2": f"weights rotate over {copies} copies ({copies * bytes_per_gemm / 1e6:.0f} MB > 126 MB L2)",
                    "timing": "one CUDA graph of K launches, CUDA events" if world == 1 else
+                             "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks" if not peer_mode else
                              "one CUDA graph of K steps (GEMM + peer all-gather kernel; a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
                    "parallelism": "single GPU" if world == 1 else
-                                  f"column-parallel N x{world} + all-gather over NVLink peer stores",
+                                  f"column-parallel N x{world} + all-gather over NVLink peer stores" if peer_mode else
+                                  f"column-parallel N x{world} + NCCL all-gather",
                    "rel_l2_vs_fp32_product": rel},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": TRAFFIC_BYTES_PER_LAUNCH,
