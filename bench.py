@@ -419,7 +419,7 @@ def time_graph(torch, fn, n):
     side = torch.cuda.Stream()
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(side):
-        graph.capture_begin()
+        graph.capture_begin(capture_error_mode="thread_local")
         for i in range(n):
             fn(i, side.cuda_stream)
         graph.capture_end()
