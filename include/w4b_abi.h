@@ -104,6 +104,17 @@ int w4b_device_status(void);
 /* Number of kernel launches this library has issued from the calling process. */
 unsigned long long w4b_launch_count(void);
 
+/* Launch overlap between consecutive kernels of a stream (no counterpart in the reference, whose
+ * launches are plainly stream-ordered). Off by default. When on, the stream GEMM is launched with
+ * programmatic stream serialization: its CTAs may become resident while the previous kernel of the
+ * stream is still running and pre-load the PACKED WEIGHTS (q / scales / zeros) of this call;
+ * activations, outputs and library scratch are touched only after the previous kernel has completed
+ * and its writes are visible. Turn it on only if no kernel writes a weight buffer directly before a
+ * GEMM that reads it in the same stream (weights that are uploaded once and then only read - the
+ * decode-serving case - qualify). Process-wide; returns the previous setting. */
+int w4b_set_launch_overlap(int on);
+int w4b_launch_overlap(void);
+
 /* ---- fused dequant GEMM: C[M,N] = X[M,K] * dequant(W)[N,K]^T ----------- */
 
 /* gemm / gemm_fused / gemm_mma (include/w4/dispatch.cuh:27-34,

@@ -57,6 +57,8 @@ ABI = {
     "w4b_gemm_mx_route": (_I, [C.POINTER(_PackedMx), _I, _I, _P]),
     "w4b_device_status": (_I, []),
     "w4b_launch_count": (C.c_ulonglong, []),
+    "w4b_set_launch_overlap": (_I, [_I]),
+    "w4b_launch_overlap": (_I, []),
     "w4b_gemm_w4": (_I, [C.POINTER(_PackedW4), _P, _P, _I, _I, _P, _P]),
     "w4b_gemm_mx": (_I, [C.POINTER(_PackedMx), _P, _P, _I, _I, _P, _P]),
     "w4b_gemm_w4_hostio": (_I, [C.POINTER(_PackedW4), _P, _P, _I, _I, _P]),
@@ -259,6 +261,17 @@ def device_status() -> int:
 
 def launch_count() -> int:
     return int(lib.w4b_launch_count())
+
+
+def set_launch_overlap(on: bool) -> bool:
+    """Lets consecutive stream-GEMM launches of a stream overlap (programmatic dependent launch): a launch
+    pre-loads its packed weights while the previous kernel is still running. Only for weights that no
+    kernel writes directly before the GEMM in the same stream. Returns the previous setting."""
+    return bool(lib.w4b_set_launch_overlap(1 if on else 0))
+
+
+def launch_overlap() -> bool:
+    return bool(lib.w4b_launch_overlap())
 
 
 # ---- all-gather over peer memory (no reference counterpart) ----------------------------------

@@ -19,6 +19,7 @@ using namespace w4b;
 
 thread_local char g_err[512] = "";
 std::atomic<unsigned long long> g_launches{0};
+std::atomic<int> g_overlap{0};  // w4b_set_launch_overlap
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -176,7 +177,7 @@ int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint3
     CUDA_TRY(ctx->gemm_counters.reserve(plan.counter_ints * sizeof(int), true), "gemm counters");
     CUDA_TRY(stream_gemm_launch(fmt, gs, q, scales, zeros, N, K, G, (const __half*)x, (__half*)c, M,
                                 (__half*)w_out, plan, (float*)ctx->gemm_ws.ptr, (int*)ctx->gemm_counters.ptr,
-                                ctx->status, stream),
+                                ctx->status, g_overlap.load() != 0, stream),
              who);
     g_launches += 1;
     return W4B_OK;
@@ -192,6 +193,8 @@ int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint3
 
 namespace w4b {
 void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+bool launch_overlap() { return g_overlap.load() != 0; }
+void count_launches(int n) { g_launches += (unsigned long long)n; }
 }  // namespace w4b
 
 extern "C" {
@@ -201,6 +204,10 @@ const char* w4b_last_error(void) { return g_err; }
 int w4b_dispatch_mma_min_m(void) { return kMmaMinM; }
 
 unsigned long long w4b_launch_count(void) { return g_launches.load(); }
+
+int w4b_set_launch_overlap(int on) { return g_overlap.exchange(on ? 1 : 0); }
+
+int w4b_launch_overlap(void) { return g_overlap.load(); }
 
 int w4b_device_status(void) {
   DeviceCtx* ctx = nullptr;

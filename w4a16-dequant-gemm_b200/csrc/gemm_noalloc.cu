@@ -91,7 +91,7 @@ extern "C" int w4b_gemm_w4_noalloc(const w4b_packed_w4* p, const void* x, void* 
   const cudaError_t e = stream_gemm_launch(
       p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, (const __half*)x, (__half*)c, M,
       nullptr, plan, (float*)(base + kStatusBytes + kCounterBytes), (int*)(base + kStatusBytes), (int*)base,
-      (cudaStream_t)stream);
+      launch_overlap(), (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(W4B_CUDA, cudaGetErrorString(e));
   return W4B_OK;
 }

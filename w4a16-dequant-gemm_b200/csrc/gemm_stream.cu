@@ -42,6 +42,8 @@
 // is routed to the generic kernel by the dispatcher.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "w4b_common.cuh"
 #include "w4b_kernels.h"
 
@@ -66,8 +68,19 @@ constexpr int SK_BURST = 4;  // units the producer issues back to back
 constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 2);  // ring barriers + "parked" + "collected"
 constexpr int SK_RED_BYTES_PER_MT = SK_TILES * (SK_MAX_PHASES - 1) * 32 * 16;  // cross-phase exchange
 constexpr int SK_COLLECT_BYTES_PER_MT = SK_TILES * 32 * 16;               // other CTAs' fragments, summed
+constexpr int kSmemOptIn = 232448;  // dynamic shared memory a CTA may ask for (227 KB)
+// With at most this much per CTA two CTAs fit on an SM (228 KB, 1 KB reserved per CTA): the CTA of the next
+// launch becomes resident beside this launch's and pre-loads its ring (programmatic dependent launch).
+constexpr int kSmemHalf = (233472 - 2 * 1024) / 2;
+constexpr int kMaxDevices = 64;
 
 enum : int { F_W4_SYM = 0, F_W4_ASYM = 1, F_MX = 2 };
+// W4 with 128-element groups takes the scale out of the contraction: the tensor pipe sums x * (q - z) over the
+// 128 k of one group (exact integer codes in FP16, FP32 accumulation) and the FP32 sum is multiplied by the
+// group's scale once. That is the same number as sum x * (s * (q - z)) without rounding every weight to FP16
+// first (rel L2 against the FP64 oracle 2.8e-4 instead of 2.1e-4, gate 1e-3) for 4 fewer instructions per
+// packed word. The w_out hook still emits rn16(s * (q - z)), bit-identical to dequant_one.
+__host__ __device__ constexpr bool sk_fold(int fmt, int gs) { return fmt != F_MX && gs == 128; }
 
 struct StreamParams {
   const uint32_t* q;
@@ -244,10 +257,11 @@ constexpr int BAR_TAKEN = 5;    // +tile: phase 0 has read them (phases 1..3 wai
 constexpr int BAR_XFILL = 9;    // all consumer warps: the activations are in shared memory
 
 template <int FMT, int GS, int MT, bool HOOK>
-__global__ void __launch_bounds__(sk_threads(FMT), 1)
+__global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
     stream_gemm_kernel(const __grid_constant__ CUtensorMap tmap, const StreamParams a) {
   constexpr int SK_PHASES = sk_phases(FMT);
   constexpr int SK_CONSUMERS = SK_TILES * SK_PHASES;
+  constexpr bool FOLD = sk_fold(FMT, GS);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
   const int stages = a.stages;
@@ -256,7 +270,7 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
   uint8_t* sm_q = smem;
   uint8_t* sm_meta = sm_q + (size_t)stages * SK_STAGE_Q;
   uint8_t* sm_x = sm_meta + (size_t)stages * SK_META;
-  uint8_t* sm_red = sm_x + (size_t)(a.xrows + 1) * a.xpitch;  // + one all-zero activation row
+  uint8_t* sm_red = sm_x + (size_t)a.xrows * a.xpitch;
   uint8_t* sm_collect = sm_red + MT * SK_RED_BYTES_PER_MT;
   const uint32_t sm_bar = smem_u32(sm_collect + MT * SK_COLLECT_BYTES_PER_MT);
   auto full_bar = [&](int s) { return sm_bar + 8u * (uint32_t)s; };
@@ -276,6 +290,11 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
            ((((size_t)blockIdx.y * grid + which_cta) * 2 + slot) * SK_TILES + tile_) * MT * 32;
   };
 
+  // Programmatic dependent launch (no-ops unless the launch carries the attribute): the next launch in the
+  // stream may start now - its producer warp fills its ring with weights while this grid is still running -
+  // and everything of THIS grid that reads the activations or touches c / scratch first waits for the
+  // previous grid to have completed (pdl_wait below).
+  pdl_launch_dependents();
   if (tid < stages) {
     mbar_init(full_bar(tid), 33);  // lane 0's expect_tx arrive + one cp.async arrive per producer lane
     mbar_init(empty_bar(tid), SK_TILES);  // the four tile warps of the phase that consumes the stage
@@ -302,6 +321,7 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
     // and signals `collected`. (1) is polled between bursts, (2) once every unit is issued.
     Handoff hand;  // worked out after the first burst is on its way
     bool park_done = true, collect_done = true;
+    bool prior_done = false;  // the previous grid has completed (its counters and fragments are final)
     auto tile_live = [&](int panel, int t) { return panel * SK_ROWS + t * 16 < a.N; };
     auto poll = [&](bool all_issued) {
       if (!park_done && mbar_test(parked_bar, 0u)) {
@@ -413,8 +433,15 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
         park_done = hand.park_panel < 0;
         collect_done = hand.own_panel < 0;
       }
-      poll(false);
+      // Weights are issued without waiting for the previous grid; once the ring is full (nothing more can be
+      // issued before a consumer frees a stage, and consumers start only after the previous grid) wait for it.
+      if (!prior_done && (j0 + nb >= stages || j0 + nb >= total)) {
+        pdl_wait();
+        prior_done = true;
+      }
+      if (prior_done) poll(false);
     }
+    if (!prior_done) pdl_wait();
     {  // finish the hand-offs (bounded)
       const long long t0 = clock64();
       while (!(park_done && collect_done)) {
@@ -434,7 +461,8 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
   // Activations of this pass: rows m0 .. m0+mrows-1, FP16, each row re-ordered so
   // that the 16 bytes a lane needs for word slot i of chunk `ch` are
   //   chunk (ch*32 + i*4 + c) = halves (h0,h4,h1,h5,h2,h6,h3,h7) of natural word (ch*32 + c*8 + i).
-  // Row `xrows` is all zero: lanes whose B-fragment column has no activation row read it.
+  // Lanes whose B-fragment column has no activation row never load (their registers stay zero).
+  pdl_wait();  // the activations may be the previous grid's output
   {
     const int cpr = a.K >> 3;  // 16-byte chunks per activation row
     const int total = mrows * cpr;
@@ -442,11 +470,11 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
       const int m = idx / cpr, widx = idx - m * cpr;
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)(m0 + m) * a.K) + widx);
       const int ub = widx >> 5, wi = widx & 31;
-      const int dst = (ub << 5) + ((wi & 7) << 2) + (wi >> 3);
+      // unfolded: lane c owns words 8c..8c+7, word slot i -> chunk i*4 + c;
+      // folded:   lane c owns words 4c..4c+3 of each 128-k half j, slot (j, i) -> chunk (j*4 + i)*4 + c
+      const int dst = (ub << 5) + (FOLD ? ((wi & 16) | ((wi & 3) << 2) | ((wi >> 2) & 3)) : (((wi & 7) << 2) + (wi >> 3)));
       *reinterpret_cast<uint4*>(sm_x + (size_t)m * a.xpitch + ((size_t)dst << 4)) = pair_permute(v);
     }
-    for (int idx = tid; idx < cpr; idx += 32 * SK_CONSUMERS)
-      *reinterpret_cast<uint4*>(sm_x + (size_t)a.xrows * a.xpitch + ((size_t)idx << 4)) = make_uint4(0u, 0u, 0u, 0u);
     named_barrier(BAR_XFILL, 32 * SK_CONSUMERS);
   }
 
@@ -464,8 +492,14 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
     xv[mt] = make_uint4(0u, 0u, 0u, 0u);
   }
   const W4Consts kc = w4_consts();
-  const int ra = tile * 16 + g;  // row inside the box; ra & 7 == g
-  const uint32_t sw0 = ((uint32_t)(2 * c) ^ (uint32_t)g) << 4, sw1 = ((uint32_t)(2 * c + 1) ^ (uint32_t)g) << 4;
+  // MMA row g (and g + 8) of the tile is box row rg (and rg + 8). Unfolded: rg = g, and a lane reads the
+  // 16-byte chunks 2c, 2c+1 of its rows. Folded: a lane reads chunks c and c + 4 (so that the four lanes of
+  // an MMA stay inside one 128-k group), and rg interleaves the rows (0,4,1,5,2,6,3,7) so that the two rows
+  // that share a shared-memory wavefront differ in swizzle bit 2: no bank conflicts either way.
+  const int rg = FOLD ? (((g & 1) << 2) | (g >> 1)) : g;
+  const int ra = tile * 16 + rg;  // row inside the box; ra & 7 == rg
+  const uint32_t sw0 = FOLD ? ((uint32_t)c ^ (uint32_t)rg) << 4 : ((uint32_t)(2 * c) ^ (uint32_t)rg) << 4;
+  const uint32_t sw1 = FOLD ? ((uint32_t)(c + 4) ^ (uint32_t)rg) << 4 : ((uint32_t)(2 * c + 1) ^ (uint32_t)rg) << 4;
 
   // The CTA's units are numbered j = 0, 1, ... in walk order (the ring sequence);
   // this warp handles j = phase, phase + 4, ... and tracks its ring slot incrementally.
@@ -513,37 +547,113 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
         const uint4 qb0 = *reinterpret_cast<const uint4*>(qs + 8 * 128 + sw0);
         const uint4 qb1 = *reinterpret_cast<const uint4*>(qs + 8 * 128 + sw1);
         const uint8_t* meta = sm_meta + (size_t)s_now * SK_META;
-        Groups<FMT, GS> ga, gb;
-        ga.load(meta + ra * 16, meta + SK_META_SCALES + ra * 4, c, ch);
-        gb.load(meta + (ra + 8) * 16, meta + SK_META_SCALES + (ra + 8) * 4, c, ch);
-        const uint32_t xoff = (uint32_t)ch << 9;  // 32 chunks of 16 bytes per unit
+        if constexpr (FOLD) {
+          // scales of the unit's two groups for both rows; zero points from the rows' zero words
+          const uint32_t sa2 = *reinterpret_cast<const uint32_t*>(meta + ra * 16);
+          const uint32_t sb2 = *reinterpret_cast<const uint32_t*>(meta + (ra + 8) * 16);
+          uint32_t zza = 0x88u, zzb = 0x88u;  // symmetric: z = 8 for both groups
+          if (FMT == F_W4_ASYM) {
+            const int shb = (ch & 3) << 3;  // groups 2ch, 2ch+1 -> nibbles (2ch & 7), +1 of the zero word
+            zza = *reinterpret_cast<const uint32_t*>(meta + SK_META_SCALES + ra * 4) >> shb;
+            zzb = *reinterpret_cast<const uint32_t*>(meta + SK_META_SCALES + (ra + 8) * 4) >> shb;
+          }
+          float ga_[2][MT][4];  // per group j: x * (q - z) summed over the group's 128 k
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          __half2 pa[4], pb[4];
-          ga.decode(word_of(qa0, qa1, i), i >> 2, kc, pa);
-          gb.decode(word_of(qb0, qb1, i), i >> 2, kc, pb);
-          if (HOOK && blockIdx.y == 0) {  // every pass decodes the same weights; one writes them
-            const int k = ch * SK_KC + 64 * c + 8 * i;
-            const int na = tile_row0 + g, nb = na + 8;
+          for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-              if (na < a.N) {
-                a.w_out[(size_t)na * a.K + k + jj] = __low2half(pa[jj]);
-                a.w_out[(size_t)na * a.K + k + jj + 4] = __high2half(pa[jj]);
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) ga_[j][mt][e] = 0.0f;
+          __half2 za[2], zb[2], ya[2], yb[2];  // (1024 + z) and -(64 + z), rows a / b, groups 0 / 1
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const uint32_t z_a = (zza >> (4 * j)) & 0xFu, z_b = (zzb >> (4 * j)) & 0xFu;
+            za[j] = u32_as_h2(z_a * 0x00010001u + 0x64006400u);
+            ya[j] = u32_as_h2(z_a * 0x00100010u + 0xD400D400u);
+            zb[j] = u32_as_h2(z_b * 0x00010001u + 0x64006400u);
+            yb[j] = u32_as_h2(z_b * 0x00100010u + 0xD400D400u);
+          }
+          const uint32_t xoff = (uint32_t)ch << 9;  // 32 chunks of 16 bytes per unit
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              __half2 pa[4], pb[4];
+              dq_w4_int(word_of(qa0, qa1, 4 * j + i), za[j], ya[j], kc, pa);
+              dq_w4_int(word_of(qb0, qb1, 4 * j + i), zb[j], yb[j], kc, pb);
+              if (HOOK && blockIdx.y == 0) {  // every pass decodes the same weights; one writes them
+                const __half2 s2a = __half2half2(__ushort_as_half((unsigned short)(sa2 >> (16 * j))));
+                const __half2 s2b = __half2half2(__ushort_as_half((unsigned short)(sb2 >> (16 * j))));
+                const int k = ch * SK_KC + 128 * j + 32 * c + 8 * i;
+                const int na = tile_row0 + rg, nb = na + 8;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                  const __half2 wa = __hmul2_rn(pa[jj], s2a), wb = __hmul2_rn(pb[jj], s2b);
+                  if (na < a.N) {
+                    a.w_out[(size_t)na * a.K + k + jj] = __low2half(wa);
+                    a.w_out[(size_t)na * a.K + k + jj + 4] = __high2half(wa);
+                  }
+                  if (nb < a.N) {
+                    a.w_out[(size_t)nb * a.K + k + jj] = __low2half(wb);
+                    a.w_out[(size_t)nb * a.K + k + jj + 4] = __high2half(wb);
+                  }
+                }
               }
-              if (nb < a.N) {
-                a.w_out[(size_t)nb * a.K + k + jj] = __low2half(pb[jj]);
-                a.w_out[(size_t)nb * a.K + k + jj + 4] = __high2half(pb[jj]);
+              const uint32_t f0[4] = {h2_as_u32(pa[0]), h2_as_u32(pb[0]), h2_as_u32(pa[1]), h2_as_u32(pb[1])};
+              const uint32_t f1[4] = {h2_as_u32(pa[2]), h2_as_u32(pb[2]), h2_as_u32(pa[3]), h2_as_u32(pb[3])};
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) {
+                lds128_if(xv[mt], xrow[mt] + xoff + ((uint32_t)(4 * j + i) << 6), xok[mt]);
+                mma_16816(ga_[j][mt], f0, xv[mt].x, xv[mt].y);
+                mma_16816(ga_[j][mt], f1, xv[mt].z, xv[mt].w);
               }
             }
           }
-          const uint32_t f0[4] = {h2_as_u32(pa[0]), h2_as_u32(pb[0]), h2_as_u32(pa[1]), h2_as_u32(pb[1])};
-          const uint32_t f1[4] = {h2_as_u32(pa[2]), h2_as_u32(pb[2]), h2_as_u32(pa[3]), h2_as_u32(pb[3])};
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            lds128_if(xv[mt], xrow[mt] + xoff + ((uint32_t)i << 6), xok[mt]);
-            mma_16816(acc[mt][0], f0, xv[mt].x, xv[mt].y);
-            mma_16816(acc[mt][1], f1, xv[mt].z, xv[mt].w);
+          for (int j = 0; j < 2; ++j) {
+            const float sa = __half2float(__ushort_as_half((unsigned short)(sa2 >> (16 * j))));
+            const float sb = __half2float(__ushort_as_half((unsigned short)(sb2 >> (16 * j))));
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              acc[mt][0][0] = fmaf(sa, ga_[j][mt][0], acc[mt][0][0]);
+              acc[mt][0][1] = fmaf(sa, ga_[j][mt][1], acc[mt][0][1]);
+              acc[mt][0][2] = fmaf(sb, ga_[j][mt][2], acc[mt][0][2]);
+              acc[mt][0][3] = fmaf(sb, ga_[j][mt][3], acc[mt][0][3]);
+            }
+          }
+        } else {
+          Groups<FMT, GS> ga, gb;
+          ga.load(meta + ra * 16, meta + SK_META_SCALES + ra * 4, c, ch);
+          gb.load(meta + (ra + 8) * 16, meta + SK_META_SCALES + (ra + 8) * 4, c, ch);
+          const uint32_t xoff = (uint32_t)ch << 9;  // 32 chunks of 16 bytes per unit
+  #pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            __half2 pa[4], pb[4];
+            ga.decode(word_of(qa0, qa1, i), i >> 2, kc, pa);
+            gb.decode(word_of(qb0, qb1, i), i >> 2, kc, pb);
+            if (HOOK && blockIdx.y == 0) {  // every pass decodes the same weights; one writes them
+              const int k = ch * SK_KC + 64 * c + 8 * i;
+              const int na = tile_row0 + rg, nb = na + 8;
+  #pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                if (na < a.N) {
+                  a.w_out[(size_t)na * a.K + k + jj] = __low2half(pa[jj]);
+                  a.w_out[(size_t)na * a.K + k + jj + 4] = __high2half(pa[jj]);
+                }
+                if (nb < a.N) {
+                  a.w_out[(size_t)nb * a.K + k + jj] = __low2half(pb[jj]);
+                  a.w_out[(size_t)nb * a.K + k + jj + 4] = __high2half(pb[jj]);
+                }
+              }
+            }
+            const uint32_t f0[4] = {h2_as_u32(pa[0]), h2_as_u32(pb[0]), h2_as_u32(pa[1]), h2_as_u32(pb[1])};
+            const uint32_t f1[4] = {h2_as_u32(pa[2]), h2_as_u32(pb[2]), h2_as_u32(pa[3]), h2_as_u32(pb[3])};
+  #pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              lds128_if(xv[mt], xrow[mt] + xoff + ((uint32_t)i << 6), xok[mt]);
+              mma_16816(acc[mt][0], f0, xv[mt].x, xv[mt].y);
+              mma_16816(acc[mt][1], f1, xv[mt].z, xv[mt].w);
+            }
           }
         }
       }
@@ -620,7 +730,7 @@ __global__ void __launch_bounds__(sk_threads(FMT), 1)
       }
     }
     if (write) {
-      const int na = tile_row0 + g, nb = na + 8;
+      const int na = tile_row0 + rg, nb = na + 8;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const int col = 8 * mt + 2 * c;  // activation row within this pass
@@ -658,37 +768,55 @@ EncodeTiledFn encode_tiled() {
 }
 
 template <int FMT, int GS, int MT, bool HOOK>
-cudaError_t launch_one(const CUtensorMap& tmap, const StreamParams& sp, dim3 grid, size_t smem,
+cudaError_t launch_one(const CUtensorMap& tmap, const StreamParams& sp, dim3 grid, size_t smem, bool overlap,
                        cudaStream_t stream) {
   auto kern = stream_gemm_kernel<FMT, GS, MT, HOOK>;
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+  // The shared-memory opt-in is a per-device attribute of the function: set it once on every device used.
+  static std::atomic<bool> configured[kMaxDevices];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemOptIn);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev].store(true, std::memory_order_release);
   }
-  kern<<<grid, sk_threads(FMT), smem, stream>>>(tmap, sp);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(sk_threads(FMT));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, tmap, sp);
 }
 
 template <int FMT, int GS>
 cudaError_t launch_fmt(const CUtensorMap& tmap, const StreamParams& sp, int mt, dim3 grid, size_t smem,
-                       cudaStream_t stream) {
+                       bool overlap, cudaStream_t stream) {
   const bool hook = sp.w_out != nullptr;
   if (mt == 1)
-    return hook ? launch_one<FMT, GS, 1, true>(tmap, sp, grid, smem, stream)
-                : launch_one<FMT, GS, 1, false>(tmap, sp, grid, smem, stream);
-  return hook ? launch_one<FMT, GS, 2, true>(tmap, sp, grid, smem, stream)
-              : launch_one<FMT, GS, 2, false>(tmap, sp, grid, smem, stream);
+    return hook ? launch_one<FMT, GS, 1, true>(tmap, sp, grid, smem, overlap, stream)
+                : launch_one<FMT, GS, 1, false>(tmap, sp, grid, smem, overlap, stream);
+  return hook ? launch_one<FMT, GS, 2, true>(tmap, sp, grid, smem, overlap, stream)
+              : launch_one<FMT, GS, 2, false>(tmap, sp, grid, smem, overlap, stream);
 }
 
-constexpr int kSmemBudget = 232448 - 1024 /* alignment slack */ - SK_BAR_BYTES;
-// ring depth that fits beside `rows` activation rows (+ the zero row) and the exchange area
-constexpr int kMinStages = 7;  // a burst in flight and most of another being consumed
-int stages_for(int rows, int K) {
+// Shared memory of one CTA without the ring: alignment slack, barriers, `rows` activation rows, exchange areas.
+size_t fixed_smem(int rows, int K) {
   const int mt = rows > 8 ? 2 : 1;
-  return (kSmemBudget - (rows + 1) * (K * 2 + 64) - mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT)) /
-         (SK_STAGE_Q + SK_META);
+  return 1024 + SK_BAR_BYTES + (size_t)rows * (K * 2 + 64) +
+         (size_t)mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT);
+}
+// Ring depth that fits beside `rows` activation rows within `budget` bytes per CTA.
+constexpr int kMinStages = 7;  // a burst in flight and most of another being consumed
+int stages_for(int rows, int K, int budget = kSmemOptIn) {
+  const long long room = (long long)budget - (long long)fixed_smem(rows, K);
+  return room <= 0 ? 0 : (int)(room / (SK_STAGE_Q + SK_META));
 }
 
 }  // namespace
@@ -714,25 +842,31 @@ void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan) {
   plan->rows_per_pass = rows;
   plan->mt = rows > 8 ? 2 : 1;
   plan->passes = (M + rows - 1) / rows;
-  const int st = stages_for(rows, K);
+  // Half an SM's shared memory when a useful ring fits in it (so that the next launch's CTA can sit beside
+  // this one), else all of it.
+  int st = stages_for(rows, K, kSmemHalf);
+  if (st < kMinStages) st = stages_for(rows, K);
   plan->stages = st > SK_MAX_STAGES ? SK_MAX_STAGES : st;
   plan->P = (N + SK_ROWS - 1) / SK_ROWS;
   plan->C = K / SK_KC;
   plan->U = (long long)plan->P * plan->C;
   plan->grid_x = (int)(plan->U < sm_count ? plan->U : sm_count);
   plan->xpitch = xpitch;
-  plan->smem = 1024 + (size_t)plan->stages * (SK_STAGE_Q + SK_META) + (size_t)(rows + 1) * xpitch +
-               (size_t)plan->mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT) + SK_BAR_BYTES;
+  plan->smem = fixed_smem(rows, K) + (size_t)plan->stages * (SK_STAGE_Q + SK_META);
   plan->ws_bytes = (size_t)plan->passes * plan->grid_x * 2 * SK_TILES * plan->mt * 32 * sizeof(float4);
   plan->counter_ints = (size_t)plan->passes * plan->P * SK_TILES;
 }
 
 // Launches the stream GEMM. `fmt`: 0 = W4 symmetric, 1 = W4 asymmetric, 2 = MXFP4.
 // The caller has checked stream_gemm_supported and sized ws / counters by the plan;
-// counters are all zero between launches.
+// counters are all zero between launches. `overlap` launches with programmatic stream
+// serialization: the grid may start while the previous kernel of the stream is still running
+// and reads the packed weights (q / scales / zeros) before that kernel has completed - the
+// caller promises that the previous kernel does not write them. Activations, outputs and
+// scratch are only touched after the previous kernel has completed.
 cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
                                int N, int K, int G, const __half* x, __half* c, int M, __half* w_out,
-                               const StreamPlan& plan, float* ws, int* counters, int* status,
+                               const StreamPlan& plan, float* ws, int* counters, int* status, bool overlap,
                                cudaStream_t stream) {
   CUtensorMap tmap;
   const cuuint64_t gdim[2] = {(cuuint64_t)(K / 8), (cuuint64_t)N};
@@ -771,15 +905,15 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   const dim3 grid((unsigned)plan.grid_x, (unsigned)plan.passes);  // pass y = activation rows y*rows_per_pass ...
   switch (fmt) {
     case F_W4_SYM:
-      if (gs == 32) return launch_fmt<F_W4_SYM, 32>(tmap, sp, plan.mt, grid, plan.smem, stream);
-      if (gs == 64) return launch_fmt<F_W4_SYM, 64>(tmap, sp, plan.mt, grid, plan.smem, stream);
-      return launch_fmt<F_W4_SYM, 128>(tmap, sp, plan.mt, grid, plan.smem, stream);
+      if (gs == 32) return launch_fmt<F_W4_SYM, 32>(tmap, sp, plan.mt, grid, plan.smem, overlap, stream);
+      if (gs == 64) return launch_fmt<F_W4_SYM, 64>(tmap, sp, plan.mt, grid, plan.smem, overlap, stream);
+      return launch_fmt<F_W4_SYM, 128>(tmap, sp, plan.mt, grid, plan.smem, overlap, stream);
     case F_W4_ASYM:
-      if (gs == 32) return launch_fmt<F_W4_ASYM, 32>(tmap, sp, plan.mt, grid, plan.smem, stream);
-      if (gs == 64) return launch_fmt<F_W4_ASYM, 64>(tmap, sp, plan.mt, grid, plan.smem, stream);
-      return launch_fmt<F_W4_ASYM, 128>(tmap, sp, plan.mt, grid, plan.smem, stream);
+      if (gs == 32) return launch_fmt<F_W4_ASYM, 32>(tmap, sp, plan.mt, grid, plan.smem, overlap, stream);
+      if (gs == 64) return launch_fmt<F_W4_ASYM, 64>(tmap, sp, plan.mt, grid, plan.smem, overlap, stream);
+      return launch_fmt<F_W4_ASYM, 128>(tmap, sp, plan.mt, grid, plan.smem, overlap, stream);
     default:
-      return launch_fmt<F_MX, 32>(tmap, sp, plan.mt, grid, plan.smem, stream);
+      return launch_fmt<F_MX, 32>(tmap, sp, plan.mt, grid, plan.smem, overlap, stream);
   }
 }
 

@@ -136,6 +136,20 @@ __device__ __forceinline__ void dq_w4_word(uint32_t qw, const W4Group& g, const 
   out[3] = __hmul2_rn(__hfma2(t3, k.sixteenth, g.zb), g.s2);
 }
 
+// The integer part of the W4 decoder: out = (q - z) as exact FP16 integers, in the same pairing.
+// za = (1024 + z, 1024 + z), zb = (-(64 + z), -(64 + z)). 9 instructions per word.
+__device__ __forceinline__ void dq_w4_int(uint32_t qw, __half2 za, __half2 zb, const W4Consts& k, __half2 out[4]) {
+  const uint32_t hi = qw >> 8;
+  const __half2 t0 = u32_as_h2(and_or(qw, k.lo, k.magic));
+  const __half2 t1 = u32_as_h2(and_or(qw, k.hi, k.magic));
+  const __half2 t2 = u32_as_h2(and_or(hi, k.lo, k.magic));
+  const __half2 t3 = u32_as_h2(and_or(hi, k.hi, k.magic));
+  out[0] = __hsub2_rn(t0, za);
+  out[1] = __hfma2(t1, k.sixteenth, zb);
+  out[2] = __hsub2_rn(t2, za);
+  out[3] = __hfma2(t3, k.sixteenth, zb);
+}
+
 // Convenience form for code that decodes a handful of words.
 __device__ __forceinline__ void dq_w4_word(uint32_t qw, const W4Group& g, __half2 out[4]) {
   W4Consts k;
@@ -300,6 +314,16 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
+
+// Programmatic dependent launch. Both are no-ops in a grid that was launched without the
+// programmatic-stream-serialization attribute.
+//  launch_dependents: the next grid in the stream may be scheduled once every CTA of this grid
+//    has executed it (or exited);
+//  wait: blocks until the grid this one depends on has completed and its memory is visible.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
 __device__ __forceinline__ void mma_16816(float d[4], const uint32_t a[4], uint32_t b0,

@@ -15,6 +15,10 @@ __host__ __device__ __forceinline__ int words(int n) { return (n + 7) >> 3; }
 // ---- abi.cu ------------------------------------------------------------------
 // Sets the calling thread's message returned by w4b_last_error().
 void set_last_error(const char* msg);
+// The process-wide launch-overlap setting (w4b_set_launch_overlap).
+bool launch_overlap();
+// Adds to the count returned by w4b_launch_count().
+void count_launches(int n);
 
 // ---- dequant.cu -----------------------------------------------------------
 cudaError_t dequant_w4_launch(const uint32_t* q, const __half* scales, const uint32_t* zeros, int N, int K,
@@ -49,7 +53,7 @@ bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, cons
 void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan);
 cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
                                int N, int K, int G, const __half* x, __half* c, int M, __half* w_out,
-                               const StreamPlan& plan, float* ws, int* counters, int* status,
+                               const StreamPlan& plan, float* ws, int* counters, int* status, bool overlap,
                                cudaStream_t stream);
 
 // ---- gemm_tensor.cu ---------------------------------------------------------
