@@ -71,9 +71,9 @@ def test_mx_reference_matrix(oracle, i):
     assert np.array_equal(outs["gemm_mx"], outs[winner])
 
 
-# The stream kernel's family: K % 256 == 0, N >= 64 (ragged N tails, several panels, split panels),
+# The stream kernel's family: K % 512 == 0, N >= 64 (ragged N tails, several panels, split panels),
 # every supported group size, M across the m-tile and multi-pass boundaries.
-STREAM_SHAPES = [(64, 256), (128, 256), (200, 512), (333, 1024), (1024, 2048), (2500, 256), (4096, 4096)]
+STREAM_SHAPES = [(64, 512), (128, 512), (200, 512), (333, 1024), (1024, 2048), (2500, 512), (4096, 4096)]
 
 
 @pytest.mark.parametrize("fmt", ["sym", "asym", "mx"])

@@ -4,40 +4,50 @@
 //
 // The packed weights are the whole cost: every byte of q / scales / zeros is
 // read from HBM exactly once, and the kernel is organised so that this stream
-// never stalls.
+// never stalls and nothing else sits on the critical path.
 //
-//  * Work unit = 64 rows x 256 k of packed codes = one 8 KB 2-D TMA box
-//    (cp.async.bulk.tensor, 128-byte swizzle, no multicast). A "panel" is the
-//    C = K/256 units of 64 rows. The units of the whole matrix are numbered
-//    panel-major / chunk-fastest and cut into equal contiguous ranges, one per
-//    persistent CTA (one CTA per SM), so all SMs finish together whatever N and
-//    K are ("stream-K").
-//  * The last warp is the producer: per unit it issues the TMA box plus 4..16-byte
-//    cp.async copies of the unit's scales / zero words into a ring of up to 22
-//    stages; full/empty mbarriers hand stages over, so ~200 KB per SM are in
-//    flight from the first microsecond.
-//  * The other 4 x PH warps are consumers (PH = 2 unit phases for W4, 4 for
-//    MXFP4): warp w owns the 16-row tile (w & 3) of every PH-th unit (phase
-//    w >> 2), which keeps PH stages under computation at a time. A lane decodes packed words in registers (w4b_common.cuh: no tables,
-//    no local memory) straight into mma.sync m16n8k16 A fragments; the
-//    activations sit in shared memory, arranged once per CTA in the decoder's
-//    pairing, and are the B fragments; FP32 accumulators stay in registers
-//    across the units of a panel. On B200 the packed-half pipe issues 64 lanes
-//    per clock per SM, so the 8 half2 operations a word needs already cost 16
-//    pipe cycles per warp-word: there is no room for per-weight FP32 FMAs, and
-//    the contraction rides the tensor pipe although the kernel is
-//    bandwidth-bound.
-//  * Leaving a panel, the four phase warps of a tile add their fragments in
-//    shared memory in phase order. A panel whose K range is shared by several
-//    CTAs is finished by the CTA that owns the panel's END: the others park
-//    their FP32 fragment in a workspace slot and bump the tile's counter; the
-//    owner waits (bounded) for the counter and adds the slots in CTA order.
-//    Every CTA walks its range as [tail part, whole panels, head part], so what
-//    others wait for is produced first and what a CTA waits for is consumed
-//    last: in the common case nobody waits, and the order of the additions
-//    never depends on timing - outputs are bit-identical from run to run.
+//  * Work unit = 64 rows x 512 k of packed codes = 16 KB, fetched as two 2-D
+//    TMA boxes of 64 rows x 128 bytes (cp.async.bulk.tensor, 128-byte swizzle,
+//    no multicast). A "panel" is the C = ceil(K/512) units of 64 rows. The
+//    units of the whole matrix are numbered panel-major / chunk-fastest and cut
+//    into equal contiguous ranges, one per persistent CTA (one CTA per SM), so
+//    all SMs finish together whatever N and K are ("stream-K"). Panels are
+//    kept short (64 rows) so that a CTA's range is longer than a panel for the
+//    usual K: the parts of panels that CTAs share are then done long before
+//    their owner needs them.
+//  * The last warp is the producer: per unit it waits for a free ring stage,
+//    issues the two boxes and copies the unit's scales / zero words beside them
+//    (cp.async, a few bytes per row); full/empty mbarriers hand the stages
+//    over. It touches nothing but the packed weights, so it runs ahead of
+//    the previous kernel of the stream (see "launch overlap" below).
+//  * The other eight warps are consumers: warp w owns the 16-row tile w & 3 and
+//    the 256-k half w >> 2 of every unit. A lane decodes packed
+//    words in registers (w4b_common.cuh: no tables, no local memory) into
+//    mma.sync m16n8k16 A fragments; the activations sit in shared memory,
+//    arranged once per CTA in the decoder's pairing, and are the B fragments;
+//    FP32 accumulators stay in registers across the units of a panel. On B200
+//    the packed-half pipe issues 64 lanes per clock per SM, so the half2
+//    operations of the decode already cost most of the issue budget: there is
+//    no room for per-weight FP32 FMAs, and the contraction rides the tensor
+//    pipe although the kernel is bandwidth-bound.
+//  * Leaving a panel, the warp of the upper k half hands its fragment to the
+//    warp of the lower half through shared memory (it never waits for it).
+//    A panel whose K range is shared by several CTAs is finished by the CTA
+//    that owns the panel's END: the others park their FP32 fragment in a
+//    workspace slot and bump the tile's counter (release); the owner's warp
+//    waits (bounded) for the counter and adds the slots in CTA order. Every CTA
+//    walks its range as [tail part, whole panels, head part], so what others
+//    wait for is produced first and what a CTA waits for is consumed last: in
+//    the common case nobody waits, and the order of the additions never depends
+//    on timing - outputs are bit-identical from run to run.
+//  * Launch overlap (programmatic dependent launch, opt-in by the caller): the
+//    CTA uses at most half an SM's shared memory where a useful ring fits in it,
+//    so the next launch's CTA becomes resident beside this one and fills its
+//    ring with weights while this grid is still computing; its consumers wait
+//    for this grid to complete before they read activations or touch c /
+//    scratch.
 //
-// Shapes served: K % 256 == 0, N >= 64, W4 group size 32 / 64 / 128 (MXFP4:
+// Shapes served: K % 512 == 0, N >= 64, W4 group size 32 / 64 / 128 (MXFP4:
 // its fixed 32-element blocks), 16-byte aligned q / scales / x. Anything else
 // is routed to the generic kernel by the dispatcher.
 #include <cuda.h>
@@ -51,23 +61,23 @@ namespace w4b {
 
 namespace {
 
-constexpr int SK_ROWS = 64;                     // rows per unit: 4 tiles of 16
-constexpr int SK_KC = 256;                      // k per unit
-constexpr int SK_STAGE_Q = SK_ROWS * SK_KC / 2;  // 8192 bytes of codes per unit
-constexpr int SK_META_SCALES = SK_ROWS * 16;     // <= 8 FP16 scales or 8 E8M0 bytes per row
-constexpr int SK_META = SK_META_SCALES + SK_ROWS * 4;  // + one zero word per row
-constexpr int SK_TILES = 4;
-// Unit phases: consumer warp w owns tile (w & 3) of every PH-th unit (phase w >> 2). Measured on B200: the W4
-// decoders run best with 2 phases (8 consumer warps; 4 phases are 6 % slower at the headline shape, 6 phases
-// 12 %), the heavier MXFP4 decode with 4 (2 phases are 30 % slower there).
-constexpr int SK_MAX_PHASES = 4;
-__host__ __device__ constexpr int sk_phases(int fmt) { return fmt == 2 ? 4 : 2; }
-__host__ __device__ constexpr int sk_threads(int fmt) { return 32 * (SK_TILES * sk_phases(fmt) + 1); }
-constexpr int SK_MAX_STAGES = 22;
-constexpr int SK_BURST = 4;  // units the producer issues back to back
+constexpr int SK_ROWS = 64;                      // rows per unit: 4 tiles of 16
+constexpr int SK_KC = 256;                       // k per box (one warp's share of a unit)
+constexpr int SK_KU = 2 * SK_KC;                 // k per unit: two boxes side by side
+constexpr int SK_BOX = SK_ROWS * SK_KC / 2;      // 8192 bytes of codes per box
+constexpr int SK_STAGE_Q = 2 * SK_BOX;           // 16384 bytes of codes per unit
+constexpr int SK_META_ROW = 32;                  // <= 16 FP16 scales or 16 E8M0 bytes per row and unit
+constexpr int SK_META_ZOFF = SK_ROWS * SK_META_ROW;  // then 8 bytes of zero words per row
+constexpr int SK_META = SK_META_ZOFF + SK_ROWS * 8;
+constexpr int SK_STAGE = SK_STAGE_Q + SK_META;
+constexpr int SK_TILES = 4;                      // 16-row tiles per unit
+constexpr int SK_CONSUMERS = 2 * SK_TILES;       // consumer warps: tile x k half
+constexpr int SK_THREADS = 32 * (SK_CONSUMERS + 1);
+constexpr int SK_MAX_STAGES = 12;
 constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 2);  // ring barriers + "parked" + "collected"
-constexpr int SK_RED_BYTES_PER_MT = SK_TILES * (SK_MAX_PHASES - 1) * 32 * 16;  // cross-phase exchange
-constexpr int SK_COLLECT_BYTES_PER_MT = SK_TILES * 32 * 16;               // other CTAs' fragments, summed
+constexpr int SK_RED_BYTES_PER_MT = SK_TILES * 32 * 16;      // the upper k half's fragments, one per tile
+constexpr int SK_COLLECT_BYTES_PER_MT = SK_TILES * 32 * 16;  // other CTAs' fragments, summed
+constexpr int SK_ZERO_BYTES = 512;  // one unit's worth of 16-byte chunks for the four lanes of a column
 constexpr int kSmemOptIn = 232448;  // dynamic shared memory a CTA may ask for (227 KB)
 // With at most this much per CTA two CTAs fit on an SM (228 KB, 1 KB reserved per CTA): the CTA of the next
 // launch becomes resident beside this launch's and pre-loads its ring (programmatic dependent launch).
@@ -90,8 +100,8 @@ struct StreamParams {
   __half* c;
   __half* w_out;
   int N, K, M;
-  int G;        // scales per row: groups (W4) or 32-blocks (MX)
-  int C, P;     // 256-k chunks per row, 64-row panels
+  int G, wG;    // scales per row: groups (W4) or 32-blocks (MX); zero words per row
+  int C, P;     // 512-k units per panel (the last may be half empty), 64-row panels
   int U;        // units = P * C  (U * grid < 2^31: all unit arithmetic is 32-bit)
   int stages;
   int xrows;    // activation rows per pass (<= 8*MT); pass y covers rows y*xrows ...
@@ -159,13 +169,34 @@ struct Walk {
   }
 };
 
+// Position in the walk: unit (panel p, chunk ch), the r-th of its segment.
+struct Cursor {
+  int seg, r, len, p, ch;
+  __device__ void start(const Walk& w, int C) {
+    int ua;
+    seg = r = 0;
+    w.segment(0, C, &ua, &len);
+    p = ua / C;
+    ch = ua - p * C;
+  }
+  __device__ void next(const Walk& w, int C) {
+    ++ch;
+    if (++r == len && seg + 1 < w.nseg) {
+      int ua;
+      w.segment(++seg, C, &ua, &len);
+      p = ua / C;
+      ch = ua - p * C;
+      r = 0;
+    }
+  }
+};
+
 // What a CTA does with panels it covers only in part. It parks at most one fragment per
 // tile (the panel whose end another CTA owns) and completes at most one panel (the one
 // whose end it owns); panels it covers whole are written directly.
 struct Handoff {
   int park_panel, own_panel;  // -1: none
   int b_first, b_last;        // CTAs contributing to own_panel (this CTA is b_last)
-  __device__ Handoff() : park_panel(-1), own_panel(-1), b_first(0), b_last(0) {}
   __device__ Handoff(const Walk& w, int U, int C, int grid, int me) : park_panel(-1), own_panel(-1), b_first(0), b_last(0) {
     // only the first and the last segment of a walk can be partial panels
     for (int i = 0; i < w.nseg; i += (w.nseg > 1 ? w.nseg - 1 : 1)) {
@@ -186,17 +217,20 @@ struct Handoff {
 };
 
 template <int FMT, int GS>
-struct Groups;  // per-row decode constants of one unit: [0] for words 0-3, [1] for words 4-7
+struct Groups;  // per-row decode constants of one unit (unfolded formats): [0] for words 0-3, [1] for words 4-7
 
+// A unit's row holds 512 / GS scales (and their zero nibbles: one word for 64-element groups, two for
+// 32-element groups). The warp of k half kh decodes the half's 256 k, of which lane c owns words 8c..8c+7
+// (k = 64c .. 64c+63): with 64-element groups that is group 4kh + c of the unit, with 32-element groups the
+// groups 8kh + 2c and 8kh + 2c + 1.
 template <int GS>
 struct Groups<F_W4_SYM, GS> {
   W4Group g[2];
-  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* /*zero_row*/, int c, int /*ch*/) {
-    constexpr int NGU = SK_KC / GS;
-    const int gi = GS == 128 ? (c >> 1) : (GS == 64 ? c : 2 * c);
+  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* /*zero_row*/, int c, int kh) {
     const __half* sc = reinterpret_cast<const __half*>(meta_row);
+    const int gi = GS == 64 ? 4 * kh + c : 8 * kh + 2 * c;
     g[0] = w4_group(sc[gi], 8u);
-    g[1] = NGU == 8 ? w4_group(sc[gi + (NGU == 8 ? 1 : 0)], 8u) : g[0];
+    g[1] = GS == 32 ? w4_group(sc[gi + (GS == 32 ? 1 : 0)], 8u) : g[0];
   }
   __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts& k, __half2 out[4]) const {
     dq_w4_word(w, g[half], k, out);
@@ -206,14 +240,14 @@ struct Groups<F_W4_SYM, GS> {
 template <int GS>
 struct Groups<F_W4_ASYM, GS> {
   W4Group g[2];
-  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* zero_row, int c, int ch) {
-    constexpr int NGU = SK_KC / GS;
-    const int gi = GS == 128 ? (c >> 1) : (GS == 64 ? c : 2 * c);
+  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* zero_row, int c, int kh) {
     const __half* sc = reinterpret_cast<const __half*>(meta_row);
-    const uint32_t zw = *reinterpret_cast<const uint32_t*>(zero_row);
-    const int nib = (ch * NGU + gi) & 7;  // group index within its zero word
+    const int gi = GS == 64 ? 4 * kh + c : 8 * kh + 2 * c;
+    // 64-element groups: the unit's 8 groups are the 8 nibbles of one word; 32-element groups: word kh of two
+    const uint32_t zw = reinterpret_cast<const uint32_t*>(zero_row)[GS == 32 ? kh : 0];
+    const int nib = GS == 32 ? 2 * c : gi;
     g[0] = w4_group(sc[gi], (zw >> (4 * nib)) & 0xFu);
-    g[1] = NGU == 8 ? w4_group(sc[gi + (NGU == 8 ? 1 : 0)], (zw >> (4 * nib + 4)) & 0xFu) : g[0];
+    g[1] = GS == 32 ? w4_group(sc[gi + (GS == 32 ? 1 : 0)], (zw >> (4 * nib + 4)) & 0xFu) : g[0];
   }
   __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts& k, __half2 out[4]) const {
     dq_w4_word(w, g[half], k, out);
@@ -223,9 +257,9 @@ struct Groups<F_W4_ASYM, GS> {
 template <int GS>
 struct Groups<F_MX, GS> {
   MxBlock b[2];
-  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* /*zero_row*/, int c, int /*ch*/) {
-    b[0] = mx_block(meta_row[2 * c]);
-    b[1] = mx_block(meta_row[2 * c + 1]);
+  __device__ __forceinline__ void load(const uint8_t* meta_row, const uint8_t* /*zero_row*/, int c, int kh) {
+    b[0] = mx_block(meta_row[8 * kh + 2 * c]);
+    b[1] = mx_block(meta_row[8 * kh + 2 * c + 1]);
   }
   __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts&, __half2 out[4]) const {
     dq_mx_word(w, b[half], out);
@@ -252,15 +286,13 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 __device__ __forceinline__ void named_arrive(int id, int threads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
-constexpr int BAR_HANDED = 1;   // +tile: phases 1..3 have written their fragments (phase 0 waits)
-constexpr int BAR_TAKEN = 5;    // +tile: phase 0 has read them (phases 1..3 wait before rewriting)
-constexpr int BAR_XFILL = 9;    // all consumer warps: the activations are in shared memory
+constexpr int BAR_HANDED = 1;  // +tile: the upper k half has written its fragment (the lower half waits)
+constexpr int BAR_TAKEN = 5;   // +tile: the lower half has read it (the upper half waits before rewriting)
+constexpr int BAR_XFILL = 9;   // all consumer warps: the activations are in shared memory
 
 template <int FMT, int GS, int MT, bool HOOK>
-__global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
+__global__ void __launch_bounds__(SK_THREADS, 2)
     stream_gemm_kernel(const __grid_constant__ CUtensorMap tmap, const StreamParams a) {
-  constexpr int SK_PHASES = sk_phases(FMT);
-  constexpr int SK_CONSUMERS = SK_TILES * SK_PHASES;
   constexpr bool FOLD = sk_fold(FMT, GS);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
@@ -270,34 +302,30 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
   uint8_t* sm_q = smem;
   uint8_t* sm_meta = sm_q + (size_t)stages * SK_STAGE_Q;
   uint8_t* sm_x = sm_meta + (size_t)stages * SK_META;
-  uint8_t* sm_red = sm_x + (size_t)a.xrows * a.xpitch;
+  uint8_t* sm_zero = sm_x + (size_t)a.xrows * a.xpitch;  // SK_ZERO_BYTES of zeros: the "activations" of absent rows
+  uint8_t* sm_red = sm_zero + SK_ZERO_BYTES;
   uint8_t* sm_collect = sm_red + MT * SK_RED_BYTES_PER_MT;
   const uint32_t sm_bar = smem_u32(sm_collect + MT * SK_COLLECT_BYTES_PER_MT);
   auto full_bar = [&](int s) { return sm_bar + 8u * (uint32_t)s; };
   auto empty_bar = [&](int s) { return sm_bar + 8u * (uint32_t)(stages + s); };
-  const uint32_t parked_bar = sm_bar + 8u * (uint32_t)(2 * stages);      // 4 tile warps parked their fragment
-  const uint32_t collected_bar = parked_bar + 8u;                        // the other CTAs' fragments are summed
+  const uint32_t parked_bar = sm_bar + 8u * (uint32_t)(2 * stages);  // the 4 tiles' fragments are in the workspace
+  const uint32_t collected_bar = parked_bar + 8u;                    // the other CTAs' fragments are summed
 
   const int grid = (int)gridDim.x;
   const int m0 = (int)blockIdx.y * a.xrows;  // first activation row of this pass
   const int mrows = min(a.xrows, a.M - m0);   // rows of this pass (the last may be short)
   const int C = a.C;
   const Walk walk(unit_begin(a.U, (int)blockIdx.x, grid), unit_begin(a.U, (int)blockIdx.x + 1, grid), C);
-  // parked fragment of (CTA, slot, tile): slot 0 when the panel is the CTA's first one
-  auto slot_of = [&](int which_cta, int tile_, int panel) {
-    const int slot = (unit_begin(a.U, which_cta, grid) / C == panel) ? 0 : 1;
-    return reinterpret_cast<float4*>(a.ws) +
-           ((((size_t)blockIdx.y * grid + which_cta) * 2 + slot) * SK_TILES + tile_) * MT * 32;
-  };
+  const int total = walk.u1 - walk.u0;
 
   // Programmatic dependent launch (no-ops unless the launch carries the attribute): the next launch in the
-  // stream may start now - its producer warp fills its ring with weights while this grid is still running -
-  // and everything of THIS grid that reads the activations or touches c / scratch first waits for the
-  // previous grid to have completed (pdl_wait below).
+  // stream may start now - its producer fills its ring with weights while this grid is still running - and
+  // everything of THIS grid that reads the activations or touches c / scratch first waits for the previous
+  // grid to have completed (pdl_wait below).
   pdl_launch_dependents();
   if (tid < stages) {
     mbar_init(full_bar(tid), 33);  // lane 0's expect_tx arrive + one cp.async arrive per producer lane
-    mbar_init(empty_bar(tid), SK_TILES);  // the four tile warps of the phase that consumes the stage
+    mbar_init(empty_bar(tid), SK_CONSUMERS);  // every consumer warp hands the stage back
     if (tid == 0) {
       mbar_init(parked_bar, SK_TILES);
       mbar_init(collected_bar, 1);
@@ -307,147 +335,125 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
   if (tid == 32 * SK_CONSUMERS) tma_prefetch_desc(&tmap);
   __syncthreads();
 
+  // parked fragment of (CTA, slot, tile): slot 0 when the panel is the CTA's first one
+  auto slot_of = [&](int which_cta, int tile_, int panel) {
+    const int slot = (unit_begin(a.U, which_cta, grid) / C == panel) ? 0 : 1;
+    return reinterpret_cast<float4*>(a.ws) +
+           ((((size_t)blockIdx.y * grid + which_cta) * 2 + slot) * SK_TILES + tile_) * MT * 32;
+  };
+
   if (wid == SK_CONSUMERS) {
     // ------------------------------ producer ------------------------------
-    constexpr int NGU = FMT == F_MX ? 8 : SK_KC / GS;  // scales per row per unit
-    const int wG = words(a.G);
-    // Units are issued in bursts of SK_BURST consecutive units (adjacent 128-byte
-    // columns of the same rows): DRAM then sees 128*SK_BURST contiguous bytes per row at
-    // once instead of isolated 128-byte reads, which is what keeps its pages busy.
-    // Besides loading, this warp does the CTA's hand-offs with other CTAs, so that no consumer
-    // warp ever waits for a round trip to L2: (1) once the four tile warps have parked their
-    // fragment it fences and bumps the tiles' counters; (2) for the panel this CTA completes it
-    // waits for the other CTAs' counters, adds their fragments in CTA order into shared memory
-    // and signals `collected`. (1) is polled between bursts, (2) once every unit is issued.
-    Handoff hand;  // worked out after the first burst is on its way
-    bool park_done = true, collect_done = true;
-    bool prior_done = false;  // the previous grid has completed (its counters and fragments are final)
+    // Loading reads nothing but the packed weights, so it never waits for the previous grid.
+    // Besides loading, this warp does the CTA's hand-offs with other CTAs, so that no consumer warp ever
+    // waits for a round trip to L2: (1) once the four tile warps have parked their fragment it fences and
+    // bumps the tiles' counters; (2) for the panel this CTA completes it waits for the other CTAs' counters,
+    // adds their fragments in CTA order into shared memory and signals `collected`. (1) is polled between
+    // units, (2) once every unit is issued and the previous grid has completed (its counters are final).
+    const Handoff hand(walk, a.U, C, grid, (int)blockIdx.x);
+    bool park_done = hand.park_panel < 0, collect_done = hand.own_panel < 0;
     auto tile_live = [&](int panel, int t) { return panel * SK_ROWS + t * 16 < a.N; };
-    auto poll = [&](bool all_issued) {
+    auto poll_park = [&]() {
       if (!park_done && mbar_test(parked_bar, 0u)) {
         __threadfence();  // the parked fragments are visible before the counters move
         if (lane < SK_TILES && tile_live(hand.park_panel, lane))
           atomicAdd(a.counters + ((size_t)blockIdx.y * a.P + hand.park_panel) * SK_TILES + lane, 1);
         park_done = true;
       }
-      if (!collect_done && all_issued) {  // reading the counters costs a trip to L2: not between bursts
-        int* cnt = a.counters + ((size_t)blockIdx.y * a.P + hand.own_panel) * SK_TILES;
-        bool ready = true;
-        if (lane < SK_TILES && tile_live(hand.own_panel, lane))
-          ready = *reinterpret_cast<volatile int*>(cnt + lane) >= hand.b_last - hand.b_first;
-        if (__all_sync(0xffffffffu, ready)) {
-          __threadfence();
-          constexpr int TB = MT == 1 ? SK_TILES : 2;  // tiles whose fragments are in flight together
-#pragma unroll 1
-          for (int t0 = 0; t0 < SK_TILES; t0 += TB) {
-            float4 sum[TB][MT];
-#pragma unroll
-            for (int t = 0; t < TB; ++t)
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) sum[t][mt] = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int b = hand.b_first; b < hand.b_last; ++b) {  // fixed order: by CTA, never by arrival
-              float4 v[TB][MT];
-#pragma unroll
-              for (int t = 0; t < TB; ++t) {
-                const float4* theirs = slot_of(b, t0 + t, hand.own_panel);
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-                  v[t][mt] = tile_live(hand.own_panel, t0 + t) ? __ldcg(theirs + mt * 32 + lane)
-                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-              }
-#pragma unroll
-              for (int t = 0; t < TB; ++t)
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                  sum[t][mt].x += v[t][mt].x;
-                  sum[t][mt].y += v[t][mt].y;
-                  sum[t][mt].z += v[t][mt].z;
-                  sum[t][mt].w += v[t][mt].w;
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < TB; ++t)
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt)
-                reinterpret_cast<float4*>(sm_collect)[((t0 + t) * MT + mt) * 32 + lane] = sum[t][mt];
-          }
-          if (lane < SK_TILES) cnt[lane] = 0;  // ready for the next launch
-          __syncwarp();
-          if (lane == 0) mbar_arrive(collected_bar);
-          collect_done = true;
-        }
-      }
     };
-    const int total = walk.u1 - walk.u0;
-    int sw = 0, si = 0;            // ring slot of the next unit to wait for / to issue
-    uint32_t phw = 0;              // parity of the wait cursor
-    int seg = 0, r = 0, len = 0, p = 0, ch = 0;
-    {
-      int ua;
-      walk.segment(0, C, &ua, &len);
-      p = ua / C;
-      ch = ua - p * C;
-    }
-    for (int j0 = 0; j0 < total; j0 += SK_BURST) {
-      const int nb = min(SK_BURST, total - j0);
-      for (int b = 0; b < nb; ++b) {
-        if (!mbar_wait(empty_bar(sw), phw ^ 1u, a.status, ST_STREAM_EMPTY_TIMEOUT)) return;
-        if (++sw == stages) {
-          sw = 0;
-          phw ^= 1u;
-        }
-      }
-      for (int b = 0; b < nb; ++b) {
-        const int s = si;
-        if (++si == stages) si = 0;
-        if (lane == 0) {
-          mbar_arrive_expect_tx(full_bar(s), SK_STAGE_Q);
-          tma_load_2d(smem_u32(sm_q) + (uint32_t)s * SK_STAGE_Q, &tmap, ch * (SK_KC / 8), p * SK_ROWS, full_bar(s));
-        }
-        const uint32_t meta = smem_u32(sm_meta) + (uint32_t)s * SK_META;
+    auto poll_collect = [&]() {
+      int* cnt = a.counters + ((size_t)blockIdx.y * a.P + hand.own_panel) * SK_TILES;
+      bool ready = true;
+      if (lane < SK_TILES && tile_live(hand.own_panel, lane))
+        ready = *reinterpret_cast<volatile int*>(cnt + lane) >= hand.b_last - hand.b_first;
+      if (!__all_sync(0xffffffffu, ready)) return;
+      __threadfence();
+      constexpr int TB = MT == 1 ? SK_TILES : 2;  // tiles whose fragments are in flight together
+#pragma unroll 1
+      for (int t0 = 0; t0 < SK_TILES; t0 += TB) {
+        float4 sum[TB][MT];
 #pragma unroll
-        for (int rr = 0; rr < SK_ROWS / 32; ++rr) {
-          const int row = lane + 32 * rr;
-          const int n = min(p * SK_ROWS + row, a.N - 1);  // rows past N: any valid row, never used
-          if (FMT == F_MX) {
-            cp_async<8>(meta + row * 16, (const uint8_t*)a.scales + (size_t)n * a.G + (size_t)ch * 8);
-          } else {
-            cp_async<NGU * 2>(meta + row * 16, (const __half*)a.scales + (size_t)n * a.G + (size_t)ch * NGU);
-            if (FMT == F_W4_ASYM)
-              cp_async<4>(meta + SK_META_SCALES + row * 4, a.zeros + (size_t)n * wG + (size_t)((ch * NGU) >> 3));
+        for (int t = 0; t < TB; ++t)
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) sum[t][mt] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int b = hand.b_first; b < hand.b_last; ++b) {  // fixed order: by CTA, never by arrival
+          float4 v[TB][MT];
+#pragma unroll
+          for (int t = 0; t < TB; ++t) {
+            const float4* theirs = slot_of(b, t0 + t, hand.own_panel);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+              v[t][mt] = tile_live(hand.own_panel, t0 + t) ? __ldcg(theirs + mt * 32 + lane)
+                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
           }
+#pragma unroll
+          for (int t = 0; t < TB; ++t)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              sum[t][mt].x += v[t][mt].x;
+              sum[t][mt].y += v[t][mt].y;
+              sum[t][mt].z += v[t][mt].z;
+              sum[t][mt].w += v[t][mt].w;
+            }
         }
-        cp_async_arrive_noinc(full_bar(s));
-        // advance the walk cursor
-        ++ch;
-        if (++r == len && seg + 1 < walk.nseg) {
-          int ua;
-          walk.segment(++seg, C, &ua, &len);
-          p = ua / C;
-          ch = ua - p * C;
-          r = 0;
+#pragma unroll
+        for (int t = 0; t < TB; ++t)
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            reinterpret_cast<float4*>(sm_collect)[((t0 + t) * MT + mt) * 32 + lane] = sum[t][mt];
+      }
+      if (lane < SK_TILES) cnt[lane] = 0;  // ready for the next launch
+      __syncwarp();
+      if (lane == 0) mbar_arrive(collected_bar);
+      collect_done = true;
+    };
+    constexpr int NGU = FMT == F_MX ? SK_KU / 32 : SK_KU / GS;  // scales per row and unit
+    constexpr int SBYTES = FMT == F_MX ? NGU : 2 * NGU;        // 8 (gs 128), 16 (gs 64, MX) or 32 (gs 32) bytes
+    constexpr int ZBYTES = NGU > 8 ? 8 : 4;                    // zero words of the unit's groups
+    Cursor cur;
+    cur.start(walk, C);
+    int s = 0;
+    uint32_t ph = 0;
+    for (int j = 0; j < total; ++j) {
+      if (!mbar_wait(empty_bar(s), ph ^ 1u, a.status, ST_STREAM_EMPTY_TIMEOUT)) return;
+      if (lane == 0) {
+        const uint32_t dst = smem_u32(sm_q) + (uint32_t)s * SK_STAGE_Q;
+        mbar_arrive_expect_tx(full_bar(s), SK_STAGE_Q);
+        tma_load_2d(dst, &tmap, cur.ch * (SK_KU / 8), cur.p * SK_ROWS, full_bar(s));
+        tma_load_2d(dst + SK_BOX, &tmap, cur.ch * (SK_KU / 8) + SK_KC / 8, cur.p * SK_ROWS, full_bar(s));
+      }
+      const uint32_t meta = smem_u32(sm_meta) + (uint32_t)s * SK_META;
+      const int g0 = cur.ch * NGU;  // the unit's first group (or MX block) within the row
+#pragma unroll
+      for (int rr = 0; rr < SK_ROWS / 32; ++rr) {
+        const int row = lane + 32 * rr;
+        const int n = min(cur.p * SK_ROWS + row, a.N - 1);  // rows past N: any valid row, never used
+        const uint8_t* src = (const uint8_t*)a.scales + ((size_t)n * a.G + g0) * (FMT == F_MX ? 1 : 2);
+        if constexpr (SBYTES == 32) {
+          cp_async<16>(meta + row * SK_META_ROW, src);
+          cp_async<16>(meta + row * SK_META_ROW + 16, src + 16);
+        } else {
+          cp_async<SBYTES>(meta + row * SK_META_ROW, src);
         }
+        if (FMT == F_W4_ASYM)
+          cp_async<ZBYTES>(meta + SK_META_ZOFF + row * 8, a.zeros + (size_t)n * a.wG + (size_t)((g0 >> 3) & ~(ZBYTES / 4 - 1)));
       }
-      if (j0 == 0) {
-        hand = Handoff(walk, a.U, C, grid, (int)blockIdx.x);
-        park_done = hand.park_panel < 0;
-        collect_done = hand.own_panel < 0;
+      cp_async_arrive_noinc(full_bar(s));
+      if (++s == stages) {
+        s = 0;
+        ph ^= 1u;
       }
-      // Weights are issued without waiting for the previous grid; once the ring is full (nothing more can be
-      // issued before a consumer frees a stage, and consumers start only after the previous grid) wait for it.
-      if (!prior_done && (j0 + nb >= stages || j0 + nb >= total)) {
-        pdl_wait();
-        prior_done = true;
-      }
-      if (prior_done) poll(false);
+      cur.next(walk, C);
+      poll_park();
     }
-    if (!prior_done) pdl_wait();
+    pdl_wait();  // the counters of the panels shared with other CTAs belong to the previous grid until it is done
     {  // finish the hand-offs (bounded)
       const long long t0 = clock64();
       while (!(park_done && collect_done)) {
-        poll(true);
+        poll_park();
+        if (!collect_done) poll_collect();
         if (park_done && collect_done) break;
-        __nanosleep(100);
+        __nanosleep(64);
         if (clock64() - t0 > kWaitLimitCycles) {
           if (lane == 0) atomicExch(a.status, ST_STREAM_PANEL_TIMEOUT);
           break;
@@ -458,40 +464,8 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
   }
 
   // -------------------------------- consumers --------------------------------
-  // Activations of this pass: rows m0 .. m0+mrows-1, FP16, each row re-ordered so
-  // that the 16 bytes a lane needs for word slot i of chunk `ch` are
-  //   chunk (ch*32 + i*4 + c) = halves (h0,h4,h1,h5,h2,h6,h3,h7) of natural word (ch*32 + c*8 + i).
-  // Lanes whose B-fragment column has no activation row never load (their registers stay zero).
-  pdl_wait();  // the activations may be the previous grid's output
-  {
-    const int cpr = a.K >> 3;  // 16-byte chunks per activation row
-    const int total = mrows * cpr;
-    for (int idx = tid; idx < total; idx += 32 * SK_CONSUMERS) {
-      const int m = idx / cpr, widx = idx - m * cpr;
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)(m0 + m) * a.K) + widx);
-      const int ub = widx >> 5, wi = widx & 31;
-      // unfolded: lane c owns words 8c..8c+7, word slot i -> chunk i*4 + c;
-      // folded:   lane c owns words 4c..4c+3 of each 128-k half j, slot (j, i) -> chunk (j*4 + i)*4 + c
-      const int dst = (ub << 5) + (FOLD ? ((wi & 16) | ((wi & 3) << 2) | ((wi >> 2) & 3)) : (((wi & 7) << 2) + (wi >> 3)));
-      *reinterpret_cast<uint4*>(sm_x + (size_t)m * a.xpitch + ((size_t)dst << 4)) = pair_permute(v);
-    }
-    named_barrier(BAR_XFILL, 32 * SK_CONSUMERS);
-  }
-
-  const int tile = wid & (SK_TILES - 1), phase = wid >> 2;
+  const int tile = wid & (SK_TILES - 1), kh = wid >> 2;  // 16-row tile, 256-k half of every unit
   const int g = lane >> 2, c = lane & 3;
-  // x rows this lane supplies as B-fragment column g (and g + 8 for the second m-tile).
-  // Lanes whose column has no activation row never load: their B registers stay zero.
-  uint32_t xrow[MT];
-  bool xok[MT];
-  uint4 xv[MT];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
-    xok[mt] = (g + 8 * mt) < mrows;
-    xrow[mt] = smem_u32(sm_x) + (uint32_t)(xok[mt] ? g + 8 * mt : 0) * (uint32_t)a.xpitch + ((uint32_t)c << 4);
-    xv[mt] = make_uint4(0u, 0u, 0u, 0u);
-  }
-  const W4Consts kc = w4_consts();
   // MMA row g (and g + 8) of the tile is box row rg (and rg + 8). Unfolded: rg = g, and a lane reads the
   // 16-byte chunks 2c, 2c+1 of its rows. Folded: a lane reads chunks c and c + 4 (so that the four lanes of
   // an MMA stay inside one 128-k group), and rg interleaves the rows (0,4,1,5,2,6,3,7) so that the two rows
@@ -501,14 +475,54 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
   const uint32_t sw0 = FOLD ? ((uint32_t)c ^ (uint32_t)rg) << 4 : ((uint32_t)(2 * c) ^ (uint32_t)rg) << 4;
   const uint32_t sw1 = FOLD ? ((uint32_t)(c + 4) ^ (uint32_t)rg) << 4 : ((uint32_t)(2 * c + 1) ^ (uint32_t)rg) << 4;
 
-  // The CTA's units are numbered j = 0, 1, ... in walk order (the ring sequence);
-  // this warp handles j = phase, phase + 4, ... and tracks its ring slot incrementally.
-  int jbase = 0;       // j of the first unit of the current segment
-  int jw = phase;      // next j of this warp
-  int s = phase;       // ring slot of jw  (stages >= SK_PHASES)
-  uint32_t ph = 0;     // phase parity of that slot's full barrier
-  // A warp whose bounded wait ran out stops waiting and computing but keeps walking, so that
-  // the tile's named barriers are still met and the CTA ends instead of hanging.
+  pdl_wait();  // the activations may be the previous grid's output
+  // Activations of this pass: rows m0 .. m0+mrows-1, FP16, each row re-ordered so that the 16 bytes a lane
+  // needs for one packed word are one chunk in the decoder's pairing (h0,h4,h1,h5,h2,h6,h3,h7), and the chunks
+  // the four lanes of a column read together are adjacent:
+  //   unfolded: lane c owns words 8c..8c+7, word slot i -> chunk i*4 + c;
+  //   folded:   lane c owns words 4c..4c+3 of each 128-k half j, slot (j, i) -> chunk (j*4 + i)*4 + c.
+  {
+    const int cpr = a.K >> 3;  // 16-byte chunks per activation row
+    for (int m = 0; m < mrows; ++m) {
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)(m0 + m) * a.K);
+      uint8_t* dst_row = sm_x + (size_t)m * a.xpitch;
+      for (int w0 = tid; w0 < cpr; w0 += 4 * 32 * SK_CONSUMERS) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int widx = w0 + u * 32 * SK_CONSUMERS;
+          if (widx < cpr) v[u] = __ldg(src + widx);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int widx = w0 + u * 32 * SK_CONSUMERS;
+          if (widx < cpr) {
+            const int ub = widx >> 5, wi = widx & 31;
+            const int dst = (ub << 5) + (FOLD ? ((wi & 16) | ((wi & 3) << 2) | ((wi >> 2) & 3)) : (((wi & 7) << 2) + (wi >> 3)));
+            *reinterpret_cast<uint4*>(dst_row + ((size_t)dst << 4)) = pair_permute(v[u]);
+          }
+        }
+      }
+    }
+    if (tid < SK_ZERO_BYTES / 16) reinterpret_cast<uint4*>(sm_zero)[tid] = make_uint4(0u, 0u, 0u, 0u);
+    named_barrier(BAR_XFILL, 32 * SK_CONSUMERS);
+  }
+
+  // x rows this lane supplies as B-fragment column g (and g + 8 for the second m-tile). Lanes whose
+  // column has no activation row read the zero area instead (plain loads that the compiler is free to
+  // schedule among the decode instructions).
+  const uint8_t* xrow[MT];
+  bool xok[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    xok[mt] = (g + 8 * mt) < mrows;
+    xrow[mt] = (xok[mt] ? sm_x + (size_t)(g + 8 * mt) * a.xpitch : sm_zero) + (c << 4);
+  }
+  const W4Consts kc = w4_consts();
+  int s = 0;        // ring slot of the next unit
+  uint32_t ph = 0;  // phase parity of that slot's full barrier
+  // A warp whose bounded wait ran out stops waiting and computing but keeps handing stages back, so that
+  // the CTA ends instead of hanging.
   bool alive = true;
   for (int seg = 0; seg < walk.nseg; ++seg) {
     int ua, len;
@@ -518,8 +532,6 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
     const int tile_row0 = p * SK_ROWS + tile * 16;
     const bool live = tile_row0 < a.N;  // warp-uniform
 
-    // Two accumulator sets per m-tile (even / odd MMA of a word pair): consecutive
-    // MMAs never wait on each other's result. They are added in a fixed order.
     float acc[MT][2][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -528,42 +540,46 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][h][i] = 0.0f;
 
-    for (; jw < jbase + len; jw += SK_PHASES) {
-      const int r = jw - jbase;
+    for (int r = 0; r < len; ++r) {
       const int s_now = s;
       const uint32_t ph_now = ph;
-      s += SK_PHASES;
-      if (s >= stages) {
-        s -= stages;
+      if (++s == stages) {
+        s = 0;
         ph ^= 1u;
       }
       if (alive && !mbar_wait(full_bar(s_now), ph_now, a.status, ST_STREAM_FULL_TIMEOUT)) alive = false;
-      if (!alive) continue;
-      if (live) {
-        const int ch = ch0 + r;
-        const uint8_t* qs = sm_q + (size_t)s_now * SK_STAGE_Q + (size_t)ra * 128;
+      const int ch = 2 * (ch0 + r) + kh;  // this warp's 256-k chunk of the row
+      if (live && alive) {
+        const uint8_t* qs = sm_q + (size_t)s_now * SK_STAGE_Q + (size_t)kh * SK_BOX + (size_t)ra * 128;
+        const uint8_t* meta = sm_meta + (size_t)s_now * SK_META;
         const uint4 qa0 = *reinterpret_cast<const uint4*>(qs + sw0);
         const uint4 qa1 = *reinterpret_cast<const uint4*>(qs + sw1);
         const uint4 qb0 = *reinterpret_cast<const uint4*>(qs + 8 * 128 + sw0);
         const uint4 qb1 = *reinterpret_cast<const uint4*>(qs + 8 * 128 + sw1);
-        const uint8_t* meta = sm_meta + (size_t)s_now * SK_META;
+        const uint8_t* xu[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) xu[mt] = xrow[mt] + (xok[mt] ? ((size_t)ch << 9) : 0);  // 32 chunks of 16 bytes per unit
         if constexpr (FOLD) {
-          // scales of the unit's two groups for both rows; zero points from the rows' zero words
-          const uint32_t sa2 = *reinterpret_cast<const uint32_t*>(meta + ra * 16);
-          const uint32_t sb2 = *reinterpret_cast<const uint32_t*>(meta + (ra + 8) * 16);
+          // the unit holds 4 groups per row (8 bytes of scales, one zero word); this warp's half has two
+          const uint32_t sa2 = *reinterpret_cast<const uint32_t*>(meta + ra * SK_META_ROW + 4 * kh);
+          const uint32_t sb2 = *reinterpret_cast<const uint32_t*>(meta + (ra + 8) * SK_META_ROW + 4 * kh);
           uint32_t zza = 0x88u, zzb = 0x88u;  // symmetric: z = 8 for both groups
           if (FMT == F_W4_ASYM) {
             const int shb = (ch & 3) << 3;  // groups 2ch, 2ch+1 -> nibbles (2ch & 7), +1 of the zero word
-            zza = *reinterpret_cast<const uint32_t*>(meta + SK_META_SCALES + ra * 4) >> shb;
-            zzb = *reinterpret_cast<const uint32_t*>(meta + SK_META_SCALES + (ra + 8) * 4) >> shb;
+            zza = *reinterpret_cast<const uint32_t*>(meta + SK_META_ZOFF + ra * 8) >> shb;
+            zzb = *reinterpret_cast<const uint32_t*>(meta + SK_META_ZOFF + (ra + 8) * 8) >> shb;
           }
-          float ga_[2][MT][4];  // per group j: x * (q - z) summed over the group's 128 k
+          // per group j: x * (q - z) summed over the group's 128 k, in two independent halves (the two
+          // MMAs of a word) so that consecutive MMAs never wait for each other
+          float ga_[2][2][MT][4];
 #pragma unroll
           for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-              for (int e = 0; e < 4; ++e) ga_[j][mt][e] = 0.0f;
+              for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ga_[j][h][mt][e] = 0.0f;
           __half2 za[2], zb[2], ya[2], yb[2];  // (1024 + z) and -(64 + z), rows a / b, groups 0 / 1
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
@@ -573,7 +589,6 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
             zb[j] = u32_as_h2(z_b * 0x00010001u + 0x64006400u);
             yb[j] = u32_as_h2(z_b * 0x00100010u + 0xD400D400u);
           }
-          const uint32_t xoff = (uint32_t)ch << 9;  // 32 chunks of 16 bytes per unit
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
 #pragma unroll
@@ -603,9 +618,9 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
               const uint32_t f1[4] = {h2_as_u32(pa[2]), h2_as_u32(pb[2]), h2_as_u32(pa[3]), h2_as_u32(pb[3])};
 #pragma unroll
               for (int mt = 0; mt < MT; ++mt) {
-                lds128_if(xv[mt], xrow[mt] + xoff + ((uint32_t)(4 * j + i) << 6), xok[mt]);
-                mma_16816(ga_[j][mt], f0, xv[mt].x, xv[mt].y);
-                mma_16816(ga_[j][mt], f1, xv[mt].z, xv[mt].w);
+                const uint4 xv = *reinterpret_cast<const uint4*>(xu[mt] + ((4 * j + i) << 6));
+                mma_16816(ga_[j][0][mt], f0, xv.x, xv.y);
+                mma_16816(ga_[j][1][mt], f1, xv.z, xv.w);
               }
             }
           }
@@ -615,18 +630,17 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
             const float sb = __half2float(__ushort_as_half((unsigned short)(sb2 >> (16 * j))));
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-              acc[mt][0][0] = fmaf(sa, ga_[j][mt][0], acc[mt][0][0]);
-              acc[mt][0][1] = fmaf(sa, ga_[j][mt][1], acc[mt][0][1]);
-              acc[mt][0][2] = fmaf(sb, ga_[j][mt][2], acc[mt][0][2]);
-              acc[mt][0][3] = fmaf(sb, ga_[j][mt][3], acc[mt][0][3]);
+              acc[mt][0][0] = fmaf(sa, ga_[j][0][mt][0] + ga_[j][1][mt][0], acc[mt][0][0]);
+              acc[mt][0][1] = fmaf(sa, ga_[j][0][mt][1] + ga_[j][1][mt][1], acc[mt][0][1]);
+              acc[mt][0][2] = fmaf(sb, ga_[j][0][mt][2] + ga_[j][1][mt][2], acc[mt][0][2]);
+              acc[mt][0][3] = fmaf(sb, ga_[j][0][mt][3] + ga_[j][1][mt][3], acc[mt][0][3]);
             }
           }
         } else {
           Groups<FMT, GS> ga, gb;
-          ga.load(meta + ra * 16, meta + SK_META_SCALES + ra * 4, c, ch);
-          gb.load(meta + (ra + 8) * 16, meta + SK_META_SCALES + (ra + 8) * 4, c, ch);
-          const uint32_t xoff = (uint32_t)ch << 9;  // 32 chunks of 16 bytes per unit
-  #pragma unroll
+          ga.load(meta + ra * SK_META_ROW, meta + SK_META_ZOFF + ra * 8, c, kh);
+          gb.load(meta + (ra + 8) * SK_META_ROW, meta + SK_META_ZOFF + (ra + 8) * 8, c, kh);
+#pragma unroll
           for (int i = 0; i < 8; ++i) {
             __half2 pa[4], pb[4];
             ga.decode(word_of(qa0, qa1, i), i >> 2, kc, pa);
@@ -634,7 +648,7 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
             if (HOOK && blockIdx.y == 0) {  // every pass decodes the same weights; one writes them
               const int k = ch * SK_KC + 64 * c + 8 * i;
               const int na = tile_row0 + rg, nb = na + 8;
-  #pragma unroll
+#pragma unroll
               for (int jj = 0; jj < 4; ++jj) {
                 if (na < a.N) {
                   a.w_out[(size_t)na * a.K + k + jj] = __low2half(pa[jj]);
@@ -648,11 +662,11 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
             }
             const uint32_t f0[4] = {h2_as_u32(pa[0]), h2_as_u32(pb[0]), h2_as_u32(pa[1]), h2_as_u32(pb[1])};
             const uint32_t f1[4] = {h2_as_u32(pa[2]), h2_as_u32(pb[2]), h2_as_u32(pa[3]), h2_as_u32(pb[3])};
-  #pragma unroll
+#pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-              lds128_if(xv[mt], xrow[mt] + xoff + ((uint32_t)i << 6), xok[mt]);
-              mma_16816(acc[mt][0], f0, xv[mt].x, xv[mt].y);
-              mma_16816(acc[mt][1], f1, xv[mt].z, xv[mt].w);
+              const uint4 xv = *reinterpret_cast<const uint4*>(xu[mt] + (i << 6));
+              mma_16816(acc[mt][0], f0, xv.x, xv.y);
+              mma_16816(acc[mt][1], f1, xv.z, xv.w);
             }
           }
         }
@@ -660,7 +674,6 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s_now));
     }
-    jbase += len;
 
     // ---- the CTA leaves panel p having covered chunks [ch0, ch0 + len) ----
     float out[MT][4];
@@ -668,68 +681,60 @@ __global__ void __launch_bounds__(sk_threads(FMT), FMT == F_MX ? 1 : 2)
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) out[mt][i] = acc[mt][0][i] + acc[mt][1][i];
-    // the four phase warps of the tile: phases 1..3 hand their fragment to phase 0
-    float4* red = reinterpret_cast<float4*>(sm_red) + (size_t)(tile * (SK_PHASES - 1)) * MT * 32;
-    // Phases 1..3 never wait for phase 0 here unless it is a whole segment behind: they
-    // write, signal and go on to the next segment while phase 0 sums and hands the result on.
-    if (phase != 0) {
-      if (seg > 0) named_barrier(BAR_TAKEN + tile, 32 * SK_PHASES);  // phase 0 has read the previous fragments
+    // The two k halves of the tile: the upper hands its fragment to the lower. It writes, signals and goes on
+    // to the next segment; it only waits if the lower half has not yet read the previous segment's fragment.
+    // Every segment runs this protocol, dead tiles and timed-out warps included, so the barriers always pair up.
+    float4* red = reinterpret_cast<float4*>(sm_red) + (size_t)tile * MT * 32;
+    if (kh == 1) {
+      if (seg > 0) named_barrier(BAR_TAKEN + tile, 64);
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-        red[((phase - 1) * MT + mt) * 32 + lane] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
-      named_arrive(BAR_HANDED + tile, 32 * SK_PHASES);
+      for (int mt = 0; mt < MT; ++mt) red[mt * 32 + lane] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
+      named_arrive(BAR_HANDED + tile, 64);
       continue;
     }
-    named_barrier(BAR_HANDED + tile, 32 * SK_PHASES);
+    named_barrier(BAR_HANDED + tile, 64);
 #pragma unroll
-    for (int f = 0; f < SK_PHASES - 1; ++f)  // fixed order: phase 1, 2, ...
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const float4 v = red[(f * MT + mt) * 32 + lane];
-        out[mt][0] += v.x;
-        out[mt][1] += v.y;
-        out[mt][2] += v.z;
-        out[mt][3] += v.w;
-      }
-    if (seg + 1 < walk.nseg) named_arrive(BAR_TAKEN + tile, 32 * SK_PHASES);
+    for (int mt = 0; mt < MT; ++mt) {
+      const float4 v = red[mt * 32 + lane];
+      out[mt][0] += v.x;
+      out[mt][1] += v.y;
+      out[mt][2] += v.z;
+      out[mt][3] += v.w;
+    }
+    if (seg + 1 < walk.nseg) named_arrive(BAR_TAKEN + tile, 64);
+    // (only the lower-half warps get here, with the tile's complete fragment for this segment)
     const bool whole = (ch0 == 0 && len == C);  // the whole K range was ours
     const bool owner = !whole && unit_owner(a.U, (p + 1) * C - 1, grid) == (int)blockIdx.x;
-    const bool parks = !whole && !owner;
-    if (!live || !alive) {
-      if (parks && lane == 0) mbar_arrive(parked_bar);  // the count covers all four tiles
-      continue;
-    }
-
-    // (only phase-0 warps get here, with the tile's complete fragment for this segment)
-    bool write = whole;
-    if (!write) {
-      if (owner) {
-        // this CTA completes the panel: the producer warp has summed the others' fragments
-        if (!mbar_wait(collected_bar, 0u, a.status, ST_STREAM_PANEL_TIMEOUT)) {
-          alive = false;
-          continue;
-        }
-        const float4* others = reinterpret_cast<const float4*>(sm_collect) + (size_t)tile * MT * 32;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          const float4 v = others[mt * 32 + lane];
-          out[mt][0] = v.x + out[mt][0];
-          out[mt][1] = v.y + out[mt][1];
-          out[mt][2] = v.z + out[mt][2];
-          out[mt][3] = v.w + out[mt][3];
-        }
-        write = true;
-      } else {
-        // park the fragment; the producer warp publishes it, the panel's owner collects it
+    if (!whole && !owner) {
+      // park the fragment; the producer warp publishes it, the panel's owner collects it
+      if (live && alive) {
         float4* mine = slot_of((int)blockIdx.x, tile, p);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
-          mine[mt * 32 + lane] = make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(parked_bar);
+          __stcg(mine + mt * 32 + lane, make_float4(out[mt][0], out[mt][1], out[mt][2], out[mt][3]));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(parked_bar);  // the count covers all four tiles, dead or alive
+      continue;
+    }
+    if (!live || !alive) continue;
+    if (owner) {
+      // this CTA completes the panel: the producer warp has summed the others' fragments
+      if (!mbar_wait(collected_bar, 0u, a.status, ST_STREAM_PANEL_TIMEOUT)) {
+        alive = false;
+        continue;
+      }
+      const float4* others = reinterpret_cast<const float4*>(sm_collect) + (size_t)tile * MT * 32;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const float4 v = others[mt * 32 + lane];
+        out[mt][0] = v.x + out[mt][0];
+        out[mt][1] = v.y + out[mt][1];
+        out[mt][2] = v.z + out[mt][2];
+        out[mt][3] = v.w + out[mt][3];
       }
     }
-    if (write) {
+    {
       const int na = tile_row0 + rg, nb = na + 8;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
@@ -784,7 +789,7 @@ cudaError_t launch_one(const CUtensorMap& tmap, const StreamParams& sp, dim3 gri
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(sk_threads(FMT));
+  cfg.blockDim = dim3(SK_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -806,30 +811,32 @@ cudaError_t launch_fmt(const CUtensorMap& tmap, const StreamParams& sp, int mt, 
               : launch_one<FMT, GS, 2, false>(tmap, sp, grid, smem, overlap, stream);
 }
 
-// Shared memory of one CTA without the ring: alignment slack, barriers, `rows` activation rows, exchange areas.
+// Shared memory of one CTA without the ring: alignment slack, barriers, `rows` activation rows, zero area,
+// exchange areas.
 size_t fixed_smem(int rows, int K) {
   const int mt = rows > 8 ? 2 : 1;
-  return 1024 + SK_BAR_BYTES + (size_t)rows * (K * 2 + 64) +
+  return 1024 + SK_BAR_BYTES + (size_t)rows * (K * 2 + 64) + SK_ZERO_BYTES +
          (size_t)mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT);
 }
 // Ring depth that fits beside `rows` activation rows within `budget` bytes per CTA.
-constexpr int kMinStages = 7;  // a burst in flight and most of another being consumed
+constexpr int kMinStages = 3;      // one box being consumed, two in flight
+constexpr int kMinStagesHalf = 5;  // a ring worth confining to half an SM
 int stages_for(int rows, int K, int budget = kSmemOptIn) {
   const long long room = (long long)budget - (long long)fixed_smem(rows, K);
-  return room <= 0 ? 0 : (int)(room / (SK_STAGE_Q + SK_META));
+  return room <= 0 ? 0 : (int)(room / SK_STAGE);
 }
 
 }  // namespace
 
 bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, const void* scales,
                            const void* x) {
-  if (N < SK_ROWS || K < SK_KC || K % SK_KC != 0) return false;
+  if (N < SK_ROWS || K < SK_KU || K % SK_KU != 0) return false;
   if (gs_or_0_for_mx != 0 && gs_or_0_for_mx != 32 && gs_or_0_for_mx != 64 && gs_or_0_for_mx != 128)
     return false;
   if (((uintptr_t)q | (uintptr_t)scales | (uintptr_t)x) & 15u) return false;
   if (K > 65536 || stages_for(1, K) < kMinStages) return false;  // one activation row must fit beside the shortest ring
   // 32-bit unit arithmetic: units * CTAs below 2^31 (>= 100 GB of packed weights on 148 SMs)
-  if ((long long)((N + SK_ROWS - 1) / SK_ROWS) * (K / SK_KC) * 1024 >= (1LL << 31)) return false;
+  if ((long long)((N + SK_ROWS - 1) / SK_ROWS) * (K / SK_KU) * 1024 >= (1LL << 31)) return false;
   return encode_tiled() != nullptr;
 }
 
@@ -845,14 +852,14 @@ void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan) {
   // Half an SM's shared memory when a useful ring fits in it (so that the next launch's CTA can sit beside
   // this one), else all of it.
   int st = stages_for(rows, K, kSmemHalf);
-  if (st < kMinStages) st = stages_for(rows, K);
+  if (st < kMinStagesHalf) st = stages_for(rows, K);
   plan->stages = st > SK_MAX_STAGES ? SK_MAX_STAGES : st;
   plan->P = (N + SK_ROWS - 1) / SK_ROWS;
-  plan->C = K / SK_KC;
+  plan->C = K / SK_KU;
   plan->U = (long long)plan->P * plan->C;
   plan->grid_x = (int)(plan->U < sm_count ? plan->U : sm_count);
   plan->xpitch = xpitch;
-  plan->smem = fixed_smem(rows, K) + (size_t)plan->stages * (SK_STAGE_Q + SK_META);
+  plan->smem = fixed_smem(rows, K) + (size_t)plan->stages * SK_STAGE;
   plan->ws_bytes = (size_t)plan->passes * plan->grid_x * 2 * SK_TILES * plan->mt * 32 * sizeof(float4);
   plan->counter_ints = (size_t)plan->passes * plan->P * SK_TILES;
 }
@@ -871,7 +878,7 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   CUtensorMap tmap;
   const cuuint64_t gdim[2] = {(cuuint64_t)(K / 8), (cuuint64_t)N};
   const cuuint64_t gstride[1] = {(cuuint64_t)(K / 8) * 4};
-  const cuuint32_t box[2] = {SK_KC / 8, SK_ROWS};
+  const cuuint32_t box[2] = {SK_KC / 8, SK_ROWS};  // 32 words = 128 bytes wide: the swizzle span
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = encode_tiled()(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)q, gdim, gstride, box, estr,
                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -889,14 +896,11 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   sp.K = K;
   sp.M = M;
   sp.G = G;
+  sp.wG = words(G);
   sp.C = plan.C;
   sp.P = plan.P;
   sp.U = (int)plan.U;
-  // A multiple of the format's phase count: a ring slot is then always consumed by the same phase, so a warp
-  // waits for fill n of a slot only after it has itself consumed fill n - 1 (an mbarrier phase may be awaited
-  // at most one phase ahead). (The plan's shared-memory size covers the unrounded depth.)
-  sp.stages = fmt == F_MX ? plan.stages / sk_phases(F_MX) * sk_phases(F_MX)
-                          : plan.stages / sk_phases(F_W4_SYM) * sk_phases(F_W4_SYM);
+  sp.stages = plan.stages;
   sp.xpitch = plan.xpitch;
   sp.ws = ws;
   sp.counters = counters;
