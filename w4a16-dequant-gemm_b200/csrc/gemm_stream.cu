@@ -15,7 +15,7 @@
 //    kept short (64 rows) so that a CTA's range is longer than a panel for the
 //    usual K: the parts of panels that CTAs share are then done long before
 //    their owner needs them.
-//  * The last warp is the producer: per unit it waits for a free ring stage,
+//  * One warp is the loader: per unit it waits for a free ring stage,
 //    issues the two boxes and copies the unit's scales / zero words beside them
 //    (cp.async, a few bytes per row); full/empty mbarriers hand the stages
 //    over. It touches nothing but the packed weights, so it runs ahead of
@@ -34,8 +34,10 @@
 //    warp of the lower half through shared memory (it never waits for it).
 //    A panel whose K range is shared by several CTAs is finished by the CTA
 //    that owns the panel's END: the others park their FP32 fragment in a
-//    workspace slot and bump the tile's counter (release); the owner's warp
-//    waits (bounded) for the counter and adds the slots in CTA order. Every CTA
+//    workspace slot, and the CTA's hand-off warp publishes them (fence, counter)
+//    and, in the owner, waits (bounded) for the counters and adds the slots in
+//    CTA order into shared memory - no consumer warp and no load ever waits for
+//    a round trip to L2. Every CTA
 //    walks its range as [tail part, whole panels, head part], so what others
 //    wait for is produced first and what a CTA waits for is consumed last: in
 //    the common case nobody waits, and the order of the additions never depends
@@ -72,7 +74,9 @@ constexpr int SK_META = SK_META_ZOFF + SK_ROWS * 8;
 constexpr int SK_STAGE = SK_STAGE_Q + SK_META;
 constexpr int SK_TILES = 4;                      // 16-row tiles per unit
 constexpr int SK_CONSUMERS = 2 * SK_TILES;       // consumer warps: tile x k half
-constexpr int SK_THREADS = 32 * (SK_CONSUMERS + 1);
+constexpr int SK_LOADER = SK_CONSUMERS;          // warp that issues the loads
+constexpr int SK_HANDOFF = SK_CONSUMERS + 1;     // warp that exchanges fragments with other CTAs
+constexpr int SK_THREADS = 32 * (SK_CONSUMERS + 2);
 constexpr int SK_MAX_STAGES = 12;
 constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 2);  // ring barriers + "parked" + "collected"
 constexpr int SK_RED_BYTES_PER_MT = SK_TILES * 32 * 16;      // the upper k half's fragments, one per tile
@@ -85,11 +89,14 @@ constexpr int kSmemHalf = (233472 - 2 * 1024) / 2;
 constexpr int kMaxDevices = 64;
 
 enum : int { F_W4_SYM = 0, F_W4_ASYM = 1, F_MX = 2 };
-// W4 with 128-element groups takes the scale out of the contraction: the tensor pipe sums x * (q - z) over the
-// 128 k of one group (exact integer codes in FP16, FP32 accumulation) and the FP32 sum is multiplied by the
-// group's scale once. That is the same number as sum x * (s * (q - z)) without rounding every weight to FP16
-// first (rel L2 against the FP64 oracle 2.8e-4 instead of 2.1e-4, gate 1e-3) for 4 fewer instructions per
-// packed word. The w_out hook still emits rn16(s * (q - z)), bit-identical to dequant_one.
+// W4 with 128-element groups takes scale and zero point out of the contraction. A masked code is used as the
+// FP16 bit pattern it is: 0x000q is the (subnormal) half q * 2^-24, 0x00q0 is q * 2^-20, both exact, so the
+// tensor pipe sums x * q over the 128 k of one group straight from the packed word (one shift and four ANDs per
+// 8 weights; activations that meet the 2^-20 codes are stored divided by 16) with FP32 accumulation, and the
+// group then contributes  s * (2^24 * sum(x q) - z * sum(x))  in FP32, sum(x) per group being worked out once
+// per CTA. That is the same number as sum x * (s * (q - z)) without rounding every weight to FP16 first (rel L2
+// against the FP64 oracle 2.8e-4 instead of 2.1e-4, gate 1e-3) at less than half the instructions per packed
+// word. The w_out hook still emits rn16(s * (q - z)), bit-identical to dequant_one.
 __host__ __device__ constexpr bool sk_fold(int fmt, int gs) { return fmt != F_MX && gs == 128; }
 
 struct StreamParams {
@@ -128,11 +135,16 @@ __device__ __forceinline__ int unit_owner(int U, int t, int grid) {
 struct Walk {
   int u0, u1, pb, pe;
   int len_tail, n_full, len_head, nseg;
+  int p_tail, p_full, p_head, ch_head;  // panels of the tail / first whole / head segment, first chunk of the head
   bool single;
   __device__ Walk(int a, int b, int C) : u0(a), u1(b) {
-    pb = (u0 + C - 1) / C * C;  // first panel boundary at or after u0
-    pe = u1 / C * C;            // last panel boundary at or before u1
-    single = pb > pe;           // no boundary inside [u0, u1]: the range lies within one panel
+    p_head = u0 / C;
+    ch_head = u0 - p_head * C;
+    p_full = ch_head == 0 ? p_head : p_head + 1;
+    p_tail = u1 / C;
+    pb = p_full * C;  // first panel boundary at or after u0
+    pe = p_tail * C;  // last panel boundary at or before u1
+    single = pb > pe;  // no boundary inside [u0, u1]: the range lies within one panel
     if (single) {
       len_tail = n_full = 0;
       len_head = u1 - u0;
@@ -143,6 +155,29 @@ struct Walk {
       len_head = pb - u0;
       nseg = (len_tail > 0) + n_full + (len_head > 0);
     }
+  }
+  // segment i -> panel, first chunk and length, without a division
+  __device__ void segment_pc(int i, int C, int* p, int* ch0, int* len) const {
+    if (!single) {
+      if (len_tail > 0) {
+        if (i == 0) {
+          *p = p_tail;
+          *ch0 = 0;
+          *len = len_tail;
+          return;
+        }
+        --i;
+      }
+      if (i < n_full) {
+        *p = p_full + i;
+        *ch0 = 0;
+        *len = C;
+        return;
+      }
+    }
+    *p = p_head;
+    *ch0 = ch_head;
+    *len = len_head;
   }
   // segment i -> first unit and length (all units of a segment lie in one panel)
   __device__ void segment(int i, int C, int* ua, int* len) const {
@@ -173,19 +208,13 @@ struct Walk {
 struct Cursor {
   int seg, r, len, p, ch;
   __device__ void start(const Walk& w, int C) {
-    int ua;
     seg = r = 0;
-    w.segment(0, C, &ua, &len);
-    p = ua / C;
-    ch = ua - p * C;
+    w.segment_pc(0, C, &p, &ch, &len);
   }
   __device__ void next(const Walk& w, int C) {
     ++ch;
     if (++r == len && seg + 1 < w.nseg) {
-      int ua;
-      w.segment(++seg, C, &ua, &len);
-      p = ua / C;
-      ch = ua - p * C;
+      w.segment_pc(++seg, C, &p, &ch, &len);
       r = 0;
     }
   }
@@ -197,6 +226,7 @@ struct Cursor {
 struct Handoff {
   int park_panel, own_panel;  // -1: none
   int b_first, b_last;        // CTAs contributing to own_panel (this CTA is b_last)
+  __device__ Handoff() : park_panel(-1), own_panel(-1), b_first(0), b_last(0) {}
   __device__ Handoff(const Walk& w, int U, int C, int grid, int me) : park_panel(-1), own_panel(-1), b_first(0), b_last(0) {
     // only the first and the last segment of a walk can be partial panels
     for (int i = 0; i < w.nseg; i += (w.nseg > 1 ? w.nseg - 1 : 1)) {
@@ -303,7 +333,9 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
   uint8_t* sm_meta = sm_q + (size_t)stages * SK_STAGE_Q;
   uint8_t* sm_x = sm_meta + (size_t)stages * SK_META;
   uint8_t* sm_zero = sm_x + (size_t)a.xrows * a.xpitch;  // SK_ZERO_BYTES of zeros: the "activations" of absent rows
-  uint8_t* sm_red = sm_zero + SK_ZERO_BYTES;
+  // folded formats: sum of the activations of row m over group gidx, at [gidx][8 * MT] (FP32)
+  float* sm_xs = reinterpret_cast<float*>(sm_zero + SK_ZERO_BYTES);
+  uint8_t* sm_red = reinterpret_cast<uint8_t*>(sm_xs) + (FOLD ? (size_t)(a.K >> 7) * 8 * MT * 4 : 0);
   uint8_t* sm_collect = sm_red + MT * SK_RED_BYTES_PER_MT;
   const uint32_t sm_bar = smem_u32(sm_collect + MT * SK_COLLECT_BYTES_PER_MT);
   auto full_bar = [&](int s) { return sm_bar + 8u * (uint32_t)s; };
@@ -332,7 +364,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
     }
     mbar_init_fence();
   }
-  if (tid == 32 * SK_CONSUMERS) tma_prefetch_desc(&tmap);
+  if (tid == 32 * SK_LOADER) tma_prefetch_desc(&tmap);
   __syncthreads();
 
   // parked fragment of (CTA, slot, tile): slot 0 when the panel is the CTA's first one
@@ -342,71 +374,9 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
            ((((size_t)blockIdx.y * grid + which_cta) * 2 + slot) * SK_TILES + tile_) * MT * 32;
   };
 
-  if (wid == SK_CONSUMERS) {
-    // ------------------------------ producer ------------------------------
-    // Loading reads nothing but the packed weights, so it never waits for the previous grid.
-    // Besides loading, this warp does the CTA's hand-offs with other CTAs, so that no consumer warp ever
-    // waits for a round trip to L2: (1) once the four tile warps have parked their fragment it fences and
-    // bumps the tiles' counters; (2) for the panel this CTA completes it waits for the other CTAs' counters,
-    // adds their fragments in CTA order into shared memory and signals `collected`. (1) is polled between
-    // units, (2) once every unit is issued and the previous grid has completed (its counters are final).
-    const Handoff hand(walk, a.U, C, grid, (int)blockIdx.x);
-    bool park_done = hand.park_panel < 0, collect_done = hand.own_panel < 0;
-    auto tile_live = [&](int panel, int t) { return panel * SK_ROWS + t * 16 < a.N; };
-    auto poll_park = [&]() {
-      if (!park_done && mbar_test(parked_bar, 0u)) {
-        __threadfence();  // the parked fragments are visible before the counters move
-        if (lane < SK_TILES && tile_live(hand.park_panel, lane))
-          atomicAdd(a.counters + ((size_t)blockIdx.y * a.P + hand.park_panel) * SK_TILES + lane, 1);
-        park_done = true;
-      }
-    };
-    auto poll_collect = [&]() {
-      int* cnt = a.counters + ((size_t)blockIdx.y * a.P + hand.own_panel) * SK_TILES;
-      bool ready = true;
-      if (lane < SK_TILES && tile_live(hand.own_panel, lane))
-        ready = *reinterpret_cast<volatile int*>(cnt + lane) >= hand.b_last - hand.b_first;
-      if (!__all_sync(0xffffffffu, ready)) return;
-      __threadfence();
-      constexpr int TB = MT == 1 ? SK_TILES : 2;  // tiles whose fragments are in flight together
-#pragma unroll 1
-      for (int t0 = 0; t0 < SK_TILES; t0 += TB) {
-        float4 sum[TB][MT];
-#pragma unroll
-        for (int t = 0; t < TB; ++t)
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) sum[t][mt] = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int b = hand.b_first; b < hand.b_last; ++b) {  // fixed order: by CTA, never by arrival
-          float4 v[TB][MT];
-#pragma unroll
-          for (int t = 0; t < TB; ++t) {
-            const float4* theirs = slot_of(b, t0 + t, hand.own_panel);
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-              v[t][mt] = tile_live(hand.own_panel, t0 + t) ? __ldcg(theirs + mt * 32 + lane)
-                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-#pragma unroll
-          for (int t = 0; t < TB; ++t)
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-              sum[t][mt].x += v[t][mt].x;
-              sum[t][mt].y += v[t][mt].y;
-              sum[t][mt].z += v[t][mt].z;
-              sum[t][mt].w += v[t][mt].w;
-            }
-        }
-#pragma unroll
-        for (int t = 0; t < TB; ++t)
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-            reinterpret_cast<float4*>(sm_collect)[((t0 + t) * MT + mt) * 32 + lane] = sum[t][mt];
-      }
-      if (lane < SK_TILES) cnt[lane] = 0;  // ready for the next launch
-      __syncwarp();
-      if (lane == 0) mbar_arrive(collected_bar);
-      collect_done = true;
-    };
+  if (wid == SK_LOADER) {
+    // ------------------------------ loader ------------------------------
+    // Reads nothing but the packed weights, so it never waits for the previous grid.
     constexpr int NGU = FMT == F_MX ? SK_KU / 32 : SK_KU / GS;  // scales per row and unit
     constexpr int SBYTES = FMT == F_MX ? NGU : 2 * NGU;        // 8 (gs 128), 16 (gs 64, MX) or 32 (gs 32) bytes
     constexpr int ZBYTES = NGU > 8 ? 8 : 4;                    // zero words of the unit's groups
@@ -444,22 +414,80 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
         ph ^= 1u;
       }
       cur.next(walk, C);
-      poll_park();
     }
-    pdl_wait();  // the counters of the panels shared with other CTAs belong to the previous grid until it is done
-    {  // finish the hand-offs (bounded)
+    return;
+  }
+
+  if (wid == SK_HANDOFF) {
+    // ------------------------------ hand-offs ------------------------------
+    // This warp does the CTA's exchanges with other CTAs, so that neither a consumer warp nor the loader ever
+    // waits for a round trip to L2: (1) once the four tile warps have parked their fragment it fences and
+    // bumps the tiles' counters; (2) for the panel this CTA completes it waits for the other CTAs' counters,
+    // adds their fragments in CTA order into shared memory and signals `collected`.
+    const Handoff hand(walk, a.U, C, grid, (int)blockIdx.x);
+    auto tile_live = [&](int panel, int t) { return panel * SK_ROWS + t * 16 < a.N; };
+    if (hand.park_panel >= 0) {
+      // (the consumers park after they have waited for the previous grid)
+      if (!mbar_wait(parked_bar, 0u, a.status, ST_STREAM_PANEL_TIMEOUT)) return;
+      __threadfence();  // the parked fragments are visible before the counters move
+      if (lane < SK_TILES && tile_live(hand.park_panel, lane))
+        atomicAdd(a.counters + ((size_t)blockIdx.y * a.P + hand.park_panel) * SK_TILES + lane, 1);
+    }
+    if (hand.own_panel < 0) return;
+    pdl_wait();  // the counters of shared panels belong to the previous grid until it is done
+    int* cnt = a.counters + ((size_t)blockIdx.y * a.P + hand.own_panel) * SK_TILES;
+    {
       const long long t0 = clock64();
-      while (!(park_done && collect_done)) {
-        poll_park();
-        if (!collect_done) poll_collect();
-        if (park_done && collect_done) break;
-        __nanosleep(64);
+      for (;;) {
+        bool ready = true;
+        if (lane < SK_TILES && tile_live(hand.own_panel, lane))
+          ready = *reinterpret_cast<volatile int*>(cnt + lane) >= hand.b_last - hand.b_first;
+        if (__all_sync(0xffffffffu, ready)) break;
+        __nanosleep(100);
         if (clock64() - t0 > kWaitLimitCycles) {
           if (lane == 0) atomicExch(a.status, ST_STREAM_PANEL_TIMEOUT);
-          break;
+          return;
         }
       }
     }
+    __threadfence();
+    constexpr int TB = MT == 1 ? SK_TILES : 2;  // tiles whose fragments are in flight together
+#pragma unroll 1
+    for (int t0 = 0; t0 < SK_TILES; t0 += TB) {
+      float4 sum[TB][MT];
+#pragma unroll
+      for (int t = 0; t < TB; ++t)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) sum[t][mt] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int b = hand.b_first; b < hand.b_last; ++b) {  // fixed order: by CTA, never by arrival
+        float4 v[TB][MT];
+#pragma unroll
+        for (int t = 0; t < TB; ++t) {
+          const float4* theirs = slot_of(b, t0 + t, hand.own_panel);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            v[t][mt] = tile_live(hand.own_panel, t0 + t) ? __ldcg(theirs + mt * 32 + lane)
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int t = 0; t < TB; ++t)
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            sum[t][mt].x += v[t][mt].x;
+            sum[t][mt].y += v[t][mt].y;
+            sum[t][mt].z += v[t][mt].z;
+            sum[t][mt].w += v[t][mt].w;
+          }
+      }
+#pragma unroll
+      for (int t = 0; t < TB; ++t)
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          reinterpret_cast<float4*>(sm_collect)[((t0 + t) * MT + mt) * 32 + lane] = sum[t][mt];
+    }
+    if (lane < SK_TILES) cnt[lane] = 0;  // ready for the next launch
+    __syncwarp();
+    if (lane == 0) mbar_arrive(collected_bar);
     return;
   }
 
@@ -499,7 +527,21 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
           if (widx < cpr) {
             const int ub = widx >> 5, wi = widx & 31;
             const int dst = (ub << 5) + (FOLD ? ((wi & 16) | ((wi & 3) << 2) | ((wi >> 2) & 3)) : (((wi & 7) << 2) + (wi >> 3)));
-            *reinterpret_cast<uint4*>(dst_row + ((size_t)dst << 4)) = pair_permute(v[u]);
+            uint4 pv = pair_permute(v[u]);
+            if (FOLD) {
+              // the pairs (h1,h5) and (h3,h7) meet codes that carry 2^-20 instead of 2^-24
+              const __half2 sixteenth = u32_as_h2(0x2C002C00u);
+              pv.y = h2_as_u32(__hmul2_rn(u32_as_h2(pv.y), sixteenth));
+              pv.w = h2_as_u32(__hmul2_rn(u32_as_h2(pv.w), sixteenth));
+              // sum of the 8 activations, then of the 16 chunks of the group (16 adjacent lanes), fixed order
+              const float2 f0 = __half22float2(u32_as_h2(v[u].x)), f1 = __half22float2(u32_as_h2(v[u].y));
+              const float2 f2 = __half22float2(u32_as_h2(v[u].z)), f3 = __half22float2(u32_as_h2(v[u].w));
+              float xsum = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+#pragma unroll
+              for (int d = 1; d < 16; d <<= 1) xsum += __shfl_xor_sync(0xffffffffu, xsum, d);
+              if ((lane & 15) == 0) sm_xs[(size_t)(widx >> 4) * (8 * MT) + m] = xsum;
+            }
+            *reinterpret_cast<uint4*>(dst_row + ((size_t)dst << 4)) = pv;
           }
         }
       }
@@ -525,10 +567,8 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
   // the CTA ends instead of hanging.
   bool alive = true;
   for (int seg = 0; seg < walk.nseg; ++seg) {
-    int ua, len;
-    walk.segment(seg, C, &ua, &len);
-    const int p = ua / C;
-    const int ch0 = ua - p * C;
+    int p, ch0, len;
+    walk.segment_pc(seg, C, &p, &ch0, &len);
     const int tile_row0 = p * SK_ROWS + tile * 16;
     const bool live = tile_row0 < a.N;  // warp-uniform
 
@@ -569,71 +609,68 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
             zza = *reinterpret_cast<const uint32_t*>(meta + SK_META_ZOFF + ra * 8) >> shb;
             zzb = *reinterpret_cast<const uint32_t*>(meta + SK_META_ZOFF + (ra + 8) * 8) >> shb;
           }
-          // per group j: x * (q - z) summed over the group's 128 k, in two independent halves (the two
-          // MMAs of a word) so that consecutive MMAs never wait for each other
-          float ga_[2][2][MT][4];
+          float ga_[2][MT][4];  // per group j: 2^-24 * sum of x * q over the group's 128 k
 #pragma unroll
           for (int j = 0; j < 2; ++j)
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-              for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) ga_[j][h][mt][e] = 0.0f;
-          __half2 za[2], zb[2], ya[2], yb[2];  // (1024 + z) and -(64 + z), rows a / b, groups 0 / 1
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            const uint32_t z_a = (zza >> (4 * j)) & 0xFu, z_b = (zzb >> (4 * j)) & 0xFu;
-            za[j] = u32_as_h2(z_a * 0x00010001u + 0x64006400u);
-            ya[j] = u32_as_h2(z_a * 0x00100010u + 0xD400D400u);
-            zb[j] = u32_as_h2(z_b * 0x00010001u + 0x64006400u);
-            yb[j] = u32_as_h2(z_b * 0x00100010u + 0xD400D400u);
-          }
+              for (int e = 0; e < 4; ++e) ga_[j][mt][e] = 0.0f;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
-              __half2 pa[4], pb[4];
-              dq_w4_int(word_of(qa0, qa1, 4 * j + i), za[j], ya[j], kc, pa);
-              dq_w4_int(word_of(qb0, qb1, 4 * j + i), zb[j], yb[j], kc, pb);
+              const uint32_t wa = word_of(qa0, qa1, 4 * j + i), wb = word_of(qb0, qb1, 4 * j + i);
+              const uint32_t ha = wa >> 8, hb = wb >> 8;
+              // codes as FP16 bit patterns, rows a / b: (k0,k4) (k1,k5)/16 | (k2,k6) (k3,k7)/16 of the word
+              const uint32_t f0[4] = {wa & kc.lo, wb & kc.lo, wa & kc.hi, wb & kc.hi};
+              const uint32_t f1[4] = {ha & kc.lo, hb & kc.lo, ha & kc.hi, hb & kc.hi};
               if (HOOK && blockIdx.y == 0) {  // every pass decodes the same weights; one writes them
-                const __half2 s2a = __half2half2(__ushort_as_half((unsigned short)(sa2 >> (16 * j))));
-                const __half2 s2b = __half2half2(__ushort_as_half((unsigned short)(sb2 >> (16 * j))));
+                const W4Group wga = w4_group(__ushort_as_half((unsigned short)(sa2 >> (16 * j))), (zza >> (4 * j)) & 0xFu);
+                const W4Group wgb = w4_group(__ushort_as_half((unsigned short)(sb2 >> (16 * j))), (zzb >> (4 * j)) & 0xFu);
+                __half2 pa[4], pb[4];
+                dq_w4_word(wa, wga, kc, pa);
+                dq_w4_word(wb, wgb, kc, pb);
                 const int k = ch * SK_KC + 128 * j + 32 * c + 8 * i;
                 const int na = tile_row0 + rg, nb = na + 8;
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
-                  const __half2 wa = __hmul2_rn(pa[jj], s2a), wb = __hmul2_rn(pb[jj], s2b);
                   if (na < a.N) {
-                    a.w_out[(size_t)na * a.K + k + jj] = __low2half(wa);
-                    a.w_out[(size_t)na * a.K + k + jj + 4] = __high2half(wa);
+                    a.w_out[(size_t)na * a.K + k + jj] = __low2half(pa[jj]);
+                    a.w_out[(size_t)na * a.K + k + jj + 4] = __high2half(pa[jj]);
                   }
                   if (nb < a.N) {
-                    a.w_out[(size_t)nb * a.K + k + jj] = __low2half(wb);
-                    a.w_out[(size_t)nb * a.K + k + jj + 4] = __high2half(wb);
+                    a.w_out[(size_t)nb * a.K + k + jj] = __low2half(pb[jj]);
+                    a.w_out[(size_t)nb * a.K + k + jj + 4] = __high2half(pb[jj]);
                   }
                 }
               }
-              const uint32_t f0[4] = {h2_as_u32(pa[0]), h2_as_u32(pb[0]), h2_as_u32(pa[1]), h2_as_u32(pb[1])};
-              const uint32_t f1[4] = {h2_as_u32(pa[2]), h2_as_u32(pb[2]), h2_as_u32(pa[3]), h2_as_u32(pb[3])};
 #pragma unroll
               for (int mt = 0; mt < MT; ++mt) {
                 const uint4 xv = *reinterpret_cast<const uint4*>(xu[mt] + ((4 * j + i) << 6));
-                mma_16816(ga_[j][0][mt], f0, xv.x, xv.y);
-                mma_16816(ga_[j][1][mt], f1, xv.z, xv.w);
+                mma_16816(ga_[j][mt], f0, xv.x, xv.y);
+                mma_16816(ga_[j][mt], f1, xv.z, xv.w);
               }
             }
           }
+          // group j adds  s * (2^24 * ga - z * sum(x))  to the rows' sums
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
             const float sa = __half2float(__ushort_as_half((unsigned short)(sa2 >> (16 * j))));
             const float sb = __half2float(__ushort_as_half((unsigned short)(sb2 >> (16 * j))));
+            // z as a float: 2^23 + z has z in its low mantissa bits
+            const float fza = __uint_as_float(0x4B000000u | ((zza >> (4 * j)) & 0xFu)) - 8388608.0f;
+            const float fzb = __uint_as_float(0x4B000000u | ((zzb >> (4 * j)) & 0xFu)) - 8388608.0f;
+            const float sa24 = sa * 16777216.0f, sb24 = sb * 16777216.0f;
+            const float nza = -(sa * fza), nzb = -(sb * fzb);
+            const float* xs = sm_xs + (size_t)(2 * ch + j) * (8 * MT) + 2 * c;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-              acc[mt][0][0] = fmaf(sa, ga_[j][0][mt][0] + ga_[j][1][mt][0], acc[mt][0][0]);
-              acc[mt][0][1] = fmaf(sa, ga_[j][0][mt][1] + ga_[j][1][mt][1], acc[mt][0][1]);
-              acc[mt][0][2] = fmaf(sb, ga_[j][0][mt][2] + ga_[j][1][mt][2], acc[mt][0][2]);
-              acc[mt][0][3] = fmaf(sb, ga_[j][0][mt][3] + ga_[j][1][mt][3], acc[mt][0][3]);
+              const float2 xs2 = *reinterpret_cast<const float2*>(xs + 8 * mt);
+              acc[mt][0][0] = fmaf(nza, xs2.x, fmaf(sa24, ga_[j][mt][0], acc[mt][0][0]));
+              acc[mt][0][1] = fmaf(nza, xs2.y, fmaf(sa24, ga_[j][mt][1], acc[mt][0][1]));
+              acc[mt][0][2] = fmaf(nzb, xs2.x, fmaf(sb24, ga_[j][mt][2], acc[mt][0][2]));
+              acc[mt][0][3] = fmaf(nzb, xs2.y, fmaf(sb24, ga_[j][mt][3], acc[mt][0][3]));
             }
           }
         } else {
@@ -815,7 +852,7 @@ cudaError_t launch_fmt(const CUtensorMap& tmap, const StreamParams& sp, int mt, 
 // exchange areas.
 size_t fixed_smem(int rows, int K) {
   const int mt = rows > 8 ? 2 : 1;
-  return 1024 + SK_BAR_BYTES + (size_t)rows * (K * 2 + 64) + SK_ZERO_BYTES +
+  return 1024 + SK_BAR_BYTES + (size_t)rows * (K * 2 + 64) + SK_ZERO_BYTES + (size_t)(K / 128) * 8 * mt * 4 +
          (size_t)mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT);
 }
 // Ring depth that fits beside `rows` activation rows within `budget` bytes per CTA.
