@@ -24,12 +24,18 @@ REF_SO = os.path.join(HERE, "_ref", "libw4ref.so")
 _P = C.c_void_p
 
 
+def reference_root() -> str:
+    """Where the reference project's checkout is looked for: $W4_REFERENCE, else a directory named
+    `reference` beside this repository's checkout. It may not exist (then nothing reference-derived is built)."""
+    return os.environ.get("W4_REFERENCE") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
+
+
 def build(ref: bool = True) -> None:
     """Compile the oracle; also the reference shim when the reference tree exists."""
     subprocess.run(["make", "-C", HERE, "all"], check=True, stdout=subprocess.DEVNULL)
-    if ref and os.path.isdir(os.environ.get("W4_REFERENCE", "/root/reference")):
-        subprocess.run(["make", "-C", HERE, "ref", "REF=" + os.environ.get("W4_REFERENCE", "/root/reference")],
-                       check=True, stdout=subprocess.DEVNULL)
+    root = reference_root()
+    if ref and os.path.isfile(os.path.join(root, "include", "w4", "pack.hpp")):
+        subprocess.run(["make", "-C", HERE, "ref", "REF=" + root], check=True, stdout=subprocess.DEVNULL)
 
 
 def words(n: int) -> int:

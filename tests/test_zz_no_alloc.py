@@ -1,7 +1,7 @@
 """GPU test of w4b_gemm_w4_noalloc, the entry for callers that may not allocate
-(a stream under graph capture, a process whose memory pool owns the device, a
-serving loop with a no-allocation rule): its output must equal the regular
-entry's, on two calls in a row (the second call reuses the fixed scratch array
+(a process whose memory pool has claimed the whole device, so that cudaMalloc
+would fail, or a serving loop that forbids allocations after warm-up): its
+output must equal the regular entry's, on two calls in a row (the second call reuses the fixed scratch array
 the first one left behind). Collected last on purpose: a failure here stops a
 `-x` run only after every other test has run."""
 import numpy as np
@@ -30,6 +30,15 @@ def test_noalloc_matches_regular_entry(oracle, N, K, gs, sym, M):
         assert np.array_equal(bits(got), bits(want)), f"call {call}"
     ref = oracle.gemm_oracle(oracle.normal_f16(M * K, 22 + N), M, K, oracle.dequant_all_w4(p), N, threads=8)
     assert np.sqrt(((bits(want).view(np.float16).astype(np.float64) - ref) ** 2).sum() / (ref ** 2).sum()) <= 1e-3
+
+
+def test_noalloc_rejects_large_k_that_outgrows_the_array(oracle):
+    """K = 8192 with M = 16 halves the rows per pass: N = 1,000,000 then needs more counters than the
+    fixed array holds. Rejected on the host, before any pointer is touched (dummy pointers)."""
+    N, K, gs = 1_000_000, 8192, 128
+    desc = w4.DevicePackedW(N, K, gs, K // gs, 1, 256, 256, None)
+    with pytest.raises(w4.InvalidArgument):
+        w4.gemm_noalloc(desc, 256, 256, 16)
 
 
 def test_noalloc_rejects_what_it_cannot_serve(oracle):

@@ -218,8 +218,24 @@ int w4b_device_status(void) {
   }
   int st = 0;
   if (cudaMemcpy(&st, ctx->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -W4B_CUDA;
-  if (st != 0) cudaMemset(ctx->status, 0, sizeof(int));
-  return st;
+  // the no-allocation entry keeps its own status word (and counters) in its fixed array
+  int dev = 0, st2 = 0;
+  int* na_status = nullptr;
+  void* na_counters = nullptr;
+  size_t na_bytes = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) noalloc_regions(dev, &na_status, &na_counters, &na_bytes);
+  if (na_status && cudaMemcpy(&st2, na_status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -W4B_CUDA;
+  if (st != 0 || st2 != 0) {
+    // A kernel that gave up may have left arrival counters behind: clear them, or every later launch that
+    // shares a panel between CTAs would take stale fragments for fresh ones.
+    cudaMemset(ctx->status, 0, sizeof(int));
+    if (ctx->gemm_counters.ptr) cudaMemset(ctx->gemm_counters.ptr, 0, ctx->gemm_counters.cap);
+    if (na_status) {
+      cudaMemset(na_status, 0, sizeof(int));
+      cudaMemset(na_counters, 0, na_bytes);
+    }
+  }
+  return st != 0 ? st : st2;
 }
 
 int w4b_gemm_w4_route(const w4b_packed_w4* p, int M, int path, const void* x) {

@@ -1,27 +1,34 @@
 // w4b_gemm_w4_noalloc: the stream GEMM for callers that must not allocate.
 //
-// Who needs it: code that runs where cudaMalloc / cudaFree are off limits -
-// inside a region being captured into a CUDA graph, inside a framework whose
-// memory pool owns the whole device, or in a serving loop with a hard "no
-// allocation, no implicit device synchronisation after warm-up" rule. The
-// regular entry (w4b_gemm_w4) grows library scratch with cudaMalloc on demand;
-// this one keeps the stream kernel's scratch (the FP32 fragments of panels split
-// between CTAs, their arrival counters and the status word) in a fixed array
-// that is part of the library image. Every device that loads the library holds
-// those kNoAllocBytes until the process exits.
+// Who needs it: code that runs where cudaMalloc / cudaFree are off limits - a
+// process whose memory pool has claimed the whole device (an allocation would
+// simply fail), or a serving loop that forbids allocations and the implicit
+// device synchronisation of cudaFree once warm-up is over. The regular entry
+// (w4b_gemm_w4) grows library scratch with cudaMalloc on demand; this one keeps
+// the stream kernel's scratch (the FP32 fragments of panels split between CTAs,
+// their arrival counters and a status word) in a fixed array that is part of the
+// library image. Every device that loads the library holds those kNoAllocBytes
+// until the process exits.
 //
-// Limits: only shapes the stream kernel serves (K % 256 == 0, N >= 64, group
+// Limits: only shapes the stream kernel serves (K % 512 == 0, N >= 64, group
 // size 32 / 64 / 128, 16-byte aligned q / scales / x), and only sizes whose
-// scratch fits the array (see the two checks below; e.g. M <= 16 with
-// N <= 1,000,000 always fits on a 148-SM part). Anything else is rejected with
-// W4B_INVALID and a message; nothing falls back to an allocating path.
+// scratch fits the array: with passes = ceil(M / rows per pass) (rows per pass is
+// 16 while M * K * 2 bytes of activations fit in shared memory beside the ring,
+// fewer for long K), passes * ceil(N / 64) * 4 counters <= 65,536 and
+// passes * min(units, SMs) * 8 * (1 or 2) * 512 bytes of fragments <= 3 MiB.
+// Anything else is rejected with W4B_INVALID and a message; nothing falls back
+// to an allocating path.
 //
-// The first call on a device resolves the array's device address (and clears
-// the counters once); make that call before any stream capture. All calls share
-// the one array: calls whose kernels overlap on the GPU race on it, exactly like
-// concurrent calls of the regular entry race on the library scratch.
+// The first call on a device resolves the array's device address and clears the
+// counters with a memset on the caller's stream; make that call before any
+// stream capture. All calls share the one array, which keeps what the last call
+// left in it: the kernel re-zeroes the counters it used, and calls whose kernels
+// overlap on the GPU race on the array, exactly like concurrent calls of the
+// regular entry race on the library scratch. A bounded wait that gave up inside
+// this entry's kernel shows in w4b_device_status() like any other.
 #include "../../include/w4b_abi.h"
 
+#include <atomic>
 #include <mutex>
 
 #include "w4b_kernels.h"
@@ -38,7 +45,7 @@ constexpr size_t kNoAllocBytes = kStatusBytes + kCounterBytes + kFragmentBytes;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 constexpr int kMaxDevices = 64;
-unsigned char* g_base[kMaxDevices];
+std::atomic<unsigned char*> g_base[kMaxDevices];
 std::mutex g_mu;
 
 int fail(int code, const char* msg) {
@@ -60,7 +67,7 @@ extern "C" int w4b_gemm_w4_noalloc(const w4b_packed_w4* p, const void* x, void* 
   if (M < 1) return fail(W4B_INVALID, "gemm noalloc: bad M");
   if (!stream_gemm_supported(p->N, p->K, p->gs, p->q, p->scales, x))
     return fail(W4B_INVALID,
-                "gemm noalloc: shape not served by the stream kernel (needs K % 256 == 0, N >= 64, "
+                "gemm noalloc: shape not served by the stream kernel (needs K % 512 == 0, N >= 64, "
                 "gs in {32, 64, 128}, 16-byte aligned q / scales / x); use w4b_gemm_w4");
 
   int dev = 0, sms = 0;
@@ -75,23 +82,38 @@ extern "C" int w4b_gemm_w4_noalloc(const w4b_packed_w4* p, const void* x, void* 
   if (plan.counter_ints * sizeof(int) > kCounterBytes)
     return fail(W4B_INVALID, "gemm noalloc: N * passes too large for the fixed scratch (more than 65,536 tile counters)");
 
-  if (!g_base[dev]) {  // once per device, with that device current
+  unsigned char* base = g_base[dev].load(std::memory_order_acquire);
+  if (!base) {  // once per device, with that device current
     std::lock_guard<std::mutex> lk(g_mu);
-    if (!g_base[dev]) {
+    base = g_base[dev].load(std::memory_order_acquire);
+    if (!base) {
       unsigned char* ptr = nullptr;
       const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
       if (e != cudaSuccess || !ptr) return fail(W4B_CUDA, "gemm noalloc: cudaGetSymbolAddress failed");
-      // the counters (and the status word) must start at zero; the kernel re-zeroes what it uses
-      if (cudaMemset(ptr, 0, kStatusBytes + kCounterBytes) != cudaSuccess)
+      // the counters (and the status word) must start at zero; the kernel re-zeroes what it uses. The clear is
+      // ordered before the first kernel because it goes to the same stream.
+      if (cudaMemsetAsync(ptr, 0, kStatusBytes + kCounterBytes, (cudaStream_t)stream) != cudaSuccess)
         return fail(W4B_CUDA, "gemm noalloc: clearing the counters failed");
-      g_base[dev] = ptr;
+      g_base[dev].store(ptr, std::memory_order_release);
+      base = ptr;
     }
   }
-  unsigned char* base = g_base[dev];
   const cudaError_t e = stream_gemm_launch(
       p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, (const __half*)x, (__half*)c, M,
       nullptr, plan, (float*)(base + kStatusBytes + kCounterBytes), (int*)(base + kStatusBytes), (int*)base,
       launch_overlap(), (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(W4B_CUDA, cudaGetErrorString(e));
+  count_launches(1);
   return W4B_OK;
 }
+
+namespace w4b {
+// For w4b_device_status(): the fixed array's status word and counter region on `dev`, once the entry has been
+// used there (null before).
+void noalloc_regions(int dev, int** status, void** counters, size_t* counter_bytes) {
+  unsigned char* base = dev >= 0 && dev < kMaxDevices ? g_base[dev].load(std::memory_order_acquire) : nullptr;
+  *status = (int*)base;
+  *counters = base ? base + kStatusBytes : nullptr;
+  *counter_bytes = kCounterBytes;
+}
+}  // namespace w4b

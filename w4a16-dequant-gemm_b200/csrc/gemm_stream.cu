@@ -95,7 +95,7 @@ enum : int { F_W4_SYM = 0, F_W4_ASYM = 1, F_MX = 2 };
 // 8 weights; activations that meet the 2^-20 codes are stored divided by 16) with FP32 accumulation, and the
 // group then contributes  s * (2^24 * sum(x q) - z * sum(x))  in FP32, sum(x) per group being worked out once
 // per CTA. That is the same number as sum x * (s * (q - z)) without rounding every weight to FP16 first (rel L2
-// against the FP64 oracle 2.8e-4 instead of 2.1e-4, gate 1e-3) at less than half the instructions per packed
+// against the FP64 reference GEMM 2.8e-4 instead of 2.1e-4, gate 1e-3) at less than half the instructions per packed
 // word. The w_out hook still emits rn16(s * (q - z)), bit-identical to dequant_one.
 __host__ __device__ constexpr bool sk_fold(int fmt, int gs) { return fmt != F_MX && gs == 128; }
 

@@ -20,6 +20,9 @@ bool launch_overlap();
 // Adds to the count returned by w4b_launch_count().
 void count_launches(int n);
 
+// ---- gemm_noalloc.cu -----------------------------------------------------------
+void noalloc_regions(int dev, int** status, void** counters, size_t* counter_bytes);
+
 // ---- dequant.cu -----------------------------------------------------------
 cudaError_t dequant_w4_launch(const uint32_t* q, const __half* scales, const uint32_t* zeros, int N, int K,
                               int gs, int G, int symmetric, __half* w, cudaStream_t stream);

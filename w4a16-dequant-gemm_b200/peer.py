@@ -1,6 +1,6 @@
 """All-gather of the column-parallel GEMM's output slices over NVLink peer memory.
 
-One process per GPU. Every rank allocates an arena (two slice buffers of `world` slots each, one
+One process per GPU. Every rank allocates an arena (three slice buffers of `world` slots each, one
 64-bit flag and one 64-bit step counter per peer), exchanges its CUDA IPC handle through torch.distributed and
 maps the peers' arenas. A step is two launches on the caller's stream: the GEMM writes this rank's
 slice into its own slot, `push` stores it into every peer's slot and posts the step flag. A push
