@@ -53,6 +53,19 @@ def measured_peak():
     return 6650.0, "fallback (earlier measurement on this pool)"
 
 
+def measured_tensor_peak():
+    """Dense 16-bit tensor throughput (TFLOP/s) a kernel timed alone is held against."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["bf16_tflops"]), "measured (MEASURED_PEAKS.json, cuBLAS bf16 burst)"
+    return 1590.0, "fallback (earlier measurement on this pool)"
+
+
+def mx_bytes(N, K, M):
+    """Compulsory traffic of one MXFP4 GEMM: codes + one E8M0 byte per 32-block + activations + output."""
+    return N * ((K + 7) // 8) * 4 + N * ((K + 31) // 32) + M * K * 2 + M * N * 2
+
+
 # ---------------------------------------------------------------------------
 # clocks sampler (NVML or nvidia-smi, read-only)
 # ---------------------------------------------------------------------------
@@ -168,11 +181,46 @@ def make_w4_asym(torch, N, K, gs, seed, device):
     return qp, s.contiguous(), zp, wdeq
 
 
+def make_w4_sym(torch, N, K, gs, seed, device):
+    """W ~ N(0, 0.02), symmetric codes w = s * (q - 8) with s = amax / 7 stored in FP16."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    w = torch.randn(N, K, generator=g, device=device, dtype=torch.float32) * 0.02
+    G = K // gs
+    wg = w.view(N, G, gs)
+    amax = wg.abs().amax(-1)
+    s = torch.where(amax > 0, amax / 7.0, torch.ones_like(amax)).to(torch.float16)
+    sf = s.float()
+    q = (torch.round(wg / sf[..., None]) + 8).clamp(0, 15).to(torch.int64).view(N, K // 8, 8)
+    sh = (4 * torch.arange(8, device=device, dtype=torch.int64))
+    qp = (q << sh).sum(-1)
+    qp = torch.where(qp >= 2**31, qp - 2**32, qp).to(torch.int32).contiguous()
+    wdeq = ((q.view(N, G, gs).float() - 8.0) * sf[..., None]).to(torch.float16).view(N, K)
+    return qp, s.contiguous(), wdeq
+
+
+def make_mx(torch, N, K, seed, device):
+    """MXFP4 weights for timing and parity: uniformly random E2M1 codes and block scales 2^-9 .. 2^-6
+    (the range N(0, 0.02) weights quantise to), plus their exact dequantised values."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    codes = torch.randint(0, 16, (N, K), generator=g, device=device, dtype=torch.int64)
+    se = torch.randint(118, 122, (N, K // 32), generator=g, device=device, dtype=torch.int64)
+    sh = (4 * torch.arange(8, device=device, dtype=torch.int64))
+    qp = (codes.view(N, K // 8, 8) << sh).sum(-1)
+    qp = torch.where(qp >= 2**31, qp - 2**32, qp).to(torch.int32).contiguous()
+    mag = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], device=device)[codes & 7]
+    val = torch.where((codes & 8) != 0, -mag, mag) * torch.exp2((se - 127).float()).repeat_interleave(32, dim=1)
+    return qp, se.to(torch.uint8).contiguous(), val.to(torch.float16)
+
+
 def run_mine(args):
     import torch
     import torch.distributed as dist
 
     import w4a16_dequant_gemm_b200 as w4
+
+    # Packed weights are uploaded once and only read afterwards, so consecutive GEMM launches may overlap:
+    # a launch pre-loads its weights while the previous kernel of the stream is still running.
+    w4.set_launch_overlap(True)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -386,6 +434,9 @@ def run_mine(args):
         "config": {"workload": WORKLOAD, "us_per_gemm": round(us_per_step, 3),
                    "algorithmic_bytes_per_gemm": bytes_per_gemm,
                    "l2": f"weights rotate over {copies} copies ({copies * bytes_per_gemm / 1e6:.0f} MB > 126 MB L2)",
+                   "launch_overlap": "on (w4b_set_launch_overlap: programmatic dependent launch; a launch pre-loads "
+                                     "its packed weights while the previous one runs, activations / outputs are "
+                                     "touched only after the previous kernel has completed)",
                    "timing": "one CUDA graph of K launches, CUDA events" if world == 1 else
                              "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks" if not peer_mode else
                              "one CUDA graph of K steps (GEMM + peer all-gather kernel; a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
@@ -433,75 +484,166 @@ def time_graph(torch, fn, n):
     return 1e3 * e0.elapsed_time(e1) / n
 
 
+def rel_l2_t(torch, c, ref):
+    return float(((c.float() - ref).norm() / ref.norm()).item())
+
+
 def sweep(torch, w4, device, packs, copies):
-    """Secondary numbers of the metric: GEMM microseconds at M = 1..256 for both C2 orientations and
-    flash-decode microseconds per step (config 4, B*H = 256, S = 8192, D = 128) for FP16 / W4 / FP8."""
+    """Secondary numbers of the metric. GEMM microseconds for config 1 (W4 sym 4096 x 4096, M = 1), config 2
+    (W4 asym, both orientations, M = 1..256, ragged K = 4100), config 3 (MXFP4 8192 x 8192, M = 1..512) and the
+    per-GPU shards of config 5's four linears at M = 16, each with both roofline bounds
+    t_roof = max(bytes / HBM, 2MNK / tensor peak); flash-decode microseconds per step (config 4) for FP16 / W4 /
+    FP8 at B*H = 256, S = 8192 and at the corners, and paged W4 at 16-token pages. Inputs larger than L2 or
+    rotated over copies that are."""
     out = {"gemm_us": {}, "flash_decode_us": {}}
     peak, _ = measured_peak()
-    N, K, gs = N_ROWS, K_COLS, GS
-    for M in (1, 4, 8, 9, 16, 64, 256):
+    tpeak, _ = measured_tensor_peak()
+
+    def entry(us, nbytes, M, N, K, rel=None):
+        t_hbm, t_tc = nbytes / peak / 1e3, 2.0 * M * N * K / tpeak / 1e6  # microseconds
+        e = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
+             "frac_of_measured_hbm": round(nbytes / us / 1e3 / peak, 3), "TFLOPs": round(2.0 * M * N * K / us / 1e6, 2),
+             "roof_us": round(max(t_hbm, t_tc), 2), "bound": "hbm" if t_hbm >= t_tc else "tensor",
+             "frac_of_roof": round(max(t_hbm, t_tc) / us, 3)}
+        if rel is not None:
+            e["rel_l2_vs_fp32_product"] = float(f"{rel:.3e}")
+        return e
+
+    def time_gemm(call, descs, M, N, K, nbytes, wdeq=None):
         x = torch.randn(M, K, device=device).to(torch.float16)
         c = torch.empty(M, N, device=device, dtype=torch.float16)
+        n = len(descs)
         for i in range(3):
-            w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M)
-        us = time_graph(torch, lambda i, s: w4.gemm(packs[i % copies][3], x.data_ptr(), c.data_ptr(), M, s), 4 * copies)
-        b = alg_bytes(N, K, gs, M)
-        out["gemm_us"][f"N{N}_K{K}_M{M}"] = {"us": round(us, 2), "GBps": round(b / us / 1e3, 1),
-                                              "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3),
-                                              "TFLOPs": round(2.0 * M * N * K / us / 1e6, 2)}
+            call(descs[i % n], x.data_ptr(), c.data_ptr(), M)
+        rel = None
+        if wdeq is not None:  # descs[0] was used last at i = 0 ... recompute on it
+            call(descs[0], x.data_ptr(), c.data_ptr(), M)
+            torch.cuda.synchronize()
+            rel = rel_l2_t(torch, c, x.float() @ wdeq.float().t())
+            if not rel <= 1e-3:
+                raise SystemExit(f"bench sweep: parity failed at M={M} N={N} K={K} (rel L2 {rel:.3e})")
+        us = time_graph(torch, lambda i, s: call(descs[i % n], x.data_ptr(), c.data_ptr(), M, s), max(4 * n, 24))
+        return entry(us, nbytes, M, N, K, rel)
+
+    N, K, gs = N_ROWS, K_COLS, GS
+    descs = [p[3] for p in packs]
+    for M in (1, 4, 8, 9, 16, 64, 256):
+        out["gemm_us"][f"C2_N{N}_K{K}_M{M}"] = time_gemm(w4.gemm, descs, M, N, K, alg_bytes(N, K, gs, M))
     # the transposed orientation (N, K) = (4096, 14336)
     N2, K2 = K_COLS, N_ROWS
-    packs2 = []
+    packs2, wd2 = [], None
     for i in range(copies):
-        qp, s, zp, _ = make_w4_asym(torch, N2, K2, gs, 500 + i, device)
+        qp, s, zp, wd = make_w4_asym(torch, N2, K2, gs, 500 + i, device)
+        wd2 = wd if i == 0 else wd2
         packs2.append((qp, s, zp, w4.DevicePackedW(N2, K2, gs, K2 // gs, 0, qp.data_ptr(), s.data_ptr(), zp.data_ptr())))
-    for M in (1, 4, 16):
-        x = torch.randn(M, K2, device=device).to(torch.float16)
-        c = torch.empty(M, N2, device=device, dtype=torch.float16)
-        for i in range(3):
-            w4.gemm(packs2[i % copies][3], x.data_ptr(), c.data_ptr(), M)
-        us = time_graph(torch, lambda i, s: w4.gemm(packs2[i % copies][3], x.data_ptr(), c.data_ptr(), M, s), 4 * copies)
-        b = alg_bytes(N2, K2, gs, M)
-        out["gemm_us"][f"N{N2}_K{K2}_M{M}"] = {"us": round(us, 2), "GBps": round(b / us / 1e3, 1),
-                                                "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3)}
-    del packs2
+    for M in (1, 4, 8, 9, 16, 64, 256):
+        out["gemm_us"][f"C2_N{N2}_K{K2}_M{M}"] = time_gemm(w4.gemm, [p[3] for p in packs2], M, N2, K2,
+                                                            alg_bytes(N2, K2, gs, M), wd2 if M in (1, 16, 256) else None)
+    del packs2, wd2
+    # ragged K = 4100 (words = 513, G = 33)
+    Kr = 4100
+    Gr, wkr = (Kr + gs - 1) // gs, (Kr + 7) // 8
+    rag = []
+    for i in range(copies):
+        qp = torch.randint(-2**31, 2**31 - 1, (N, wkr), device=device, dtype=torch.int32)
+        sc = (torch.rand(N, Gr, device=device) * 0.004 + 0.002).to(torch.float16)
+        zp = torch.randint(-2**31, 2**31 - 1, (N, (Gr + 7) // 8), device=device, dtype=torch.int32)
+        rag.append((qp, sc, zp, w4.DevicePackedW(N, Kr, gs, Gr, 0, qp.data_ptr(), sc.data_ptr(), zp.data_ptr())))
+    for M in (1, 16):
+        out["gemm_us"][f"C2_ragged_N{N}_K{Kr}_M{M}"] = time_gemm(w4.gemm, [p[3] for p in rag], M, N, Kr,
+                                                                  alg_bytes(N, Kr, gs, M))
+    del rag
+    # config 1: symmetric 4096 x 4096 (8.7 MB: rotated over enough copies to exceed L2)
+    N1 = K1 = 4096
+    c1, wd1 = [], None
+    for i in range(36):
+        qp, sc, wd = make_w4_sym(torch, N1, K1, gs, 900 + i, device)
+        wd1 = wd if i == 0 else wd1
+        c1.append((qp, sc, w4.DevicePackedW(N1, K1, gs, K1 // gs, 1, qp.data_ptr(), sc.data_ptr(), None)))
+    out["gemm_us"][f"C1_sym_N{N1}_K{K1}_M1"] = time_gemm(w4.gemm, [p[2] for p in c1], 1, N1, K1,
+                                                          alg_bytes(N1, K1, gs, 1, asym=False), wd1)
+    del c1, wd1
+    # config 3: MXFP4 8192 x 8192
+    N3 = K3 = 8192
+    mx, wd3 = [], None
+    for i in range(8):
+        qp, se, wd = make_mx(torch, N3, K3, 700 + i, device)
+        wd3 = wd if i == 0 else wd3
+        mx.append((qp, se, w4.DevicePackedWm(N3, K3, K3 // 32, qp.data_ptr(), se.data_ptr())))
+    for M in (1, 8, 32, 128, 512):
+        out["gemm_us"][f"C3_mx_N{N3}_K{K3}_M{M}"] = time_gemm(w4.gemm_mx, [p[2] for p in mx], M, N3, K3,
+                                                               mx_bytes(N3, K3, M), wd3 if M in (1, 128, 512) else None)
+    del mx, wd3
+    # config 5: the per-GPU shards (N / 8) of the four linears at M = 16, W4 symmetric gs = 128
+    tot_us, tot_roof = 0.0, 0.0
+    for (Nf, K5) in ((10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672)):
+        N5 = Nf // 8
+        nb = alg_bytes(N5, K5, gs, 16, asym=False)
+        ncp = max(2, -(-300_000_000 // nb))
+        sh = []
+        for i in range(ncp):
+            qp = torch.randint(-2**31, 2**31 - 1, (N5, K5 // 8), device=device, dtype=torch.int32)
+            sc = (torch.rand(N5, K5 // gs, device=device) * 0.004 + 0.002).to(torch.float16)
+            sh.append((qp, sc, w4.DevicePackedW(N5, K5, gs, K5 // gs, 1, qp.data_ptr(), sc.data_ptr(), None)))
+        e = time_gemm(w4.gemm, [p[2] for p in sh], 16, N5, K5, nb)
+        out["gemm_us"][f"C5_shard_N{N5}_K{K5}_M16"] = e
+        tot_us += e["us"]
+        tot_roof += e["roof_us"]
+        del sh
+    out["gemm_us"]["C5_four_linears_per_gpu"] = {"us": round(tot_us, 2), "roof_us": round(tot_roof, 2),
+                                                  "frac_of_roof": round(tot_roof / tot_us, 3)}
     # flash decode: random cache bytes are as good as quantised ones for timing
-    H, S, D, g = 256, 8192, 128, 32
-    q = torch.randn(H, D, device=device).to(torch.float16)
-    o = torch.empty(H, D, device=device, dtype=torch.float16)
-    k16 = torch.randn(H, S, D, device=device).to(torch.float16)
-    v16 = torch.randn(H, S, D, device=device).to(torch.float16)
-    for i in range(2):
-        w4.attention_fp16_flash(q.data_ptr(), k16.data_ptr(), v16.data_ptr(), o.data_ptr(), H, S, D)
-    us = time_graph(torch, lambda i, s: w4.attention_fp16_flash(q.data_ptr(), k16.data_ptr(), v16.data_ptr(),
-                                                               o.data_ptr(), H, S, D, s), 5)
-    b = 2 * H * S * D * 2
-    out["flash_decode_us"]["fp16"] = {"us": round(us, 1), "GBps": round(b / us / 1e3, 1),
-                                      "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3)}
-    del k16, v16
-    G = D // g
-    qk = torch.randint(-2**31, 2**31 - 1, (H, S, D // 8), device=device, dtype=torch.int32)
-    qv = torch.randint(-2**31, 2**31 - 1, (H, S, D // 8), device=device, dtype=torch.int32)
-    sk = (torch.rand(H, S, G, device=device) * 0.1 + 0.05).to(torch.float16)
-    sv = (torch.rand(H, S, G, device=device) * 0.1 + 0.05).to(torch.float16)
-    kv = w4.DeviceKVW4(H, S, D, g, G, 1, qk.data_ptr(), sk.data_ptr(), None, qv.data_ptr(), sv.data_ptr(), None)
-    for i in range(2):
-        w4.attention_w4_flash(kv, q.data_ptr(), o.data_ptr())
-    us = time_graph(torch, lambda i, s: w4.attention_w4_flash(kv, q.data_ptr(), o.data_ptr(), s), 5)
-    b = 2 * H * S * (D // 2 + G * 2)
-    out["flash_decode_us"]["w4_gs32"] = {"us": round(us, 1), "GBps": round(b / us / 1e3, 1),
-                                         "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3)}
-    del qk, qv
-    bk = torch.randint(0, 0x7E, (H, S, D), device=device, dtype=torch.uint8)
-    bv = torch.randint(0, 0x7E, (H, S, D), device=device, dtype=torch.uint8)
-    f8 = w4.DeviceKVF8(H, S, D, g, G, bk.data_ptr(), sk.data_ptr(), bv.data_ptr(), sv.data_ptr())
-    for i in range(2):
-        w4.attention_f8_flash(f8, q.data_ptr(), o.data_ptr())
-    us = time_graph(torch, lambda i, s: w4.attention_f8_flash(f8, q.data_ptr(), o.data_ptr(), s), 5)
-    b = 2 * H * S * (D + G * 2)
-    out["flash_decode_us"]["f8_gs32"] = {"us": round(us, 1), "GBps": round(b / us / 1e3, 1),
-                                         "frac_of_measured_hbm": round(b / us / 1e3 / peak, 3)}
-    out["flash_decode_us"]["shape"] = f"B*H={H} S={S} D={D} gs={g}"
+    def flash_case(H, S, D, g, label, paged=False):
+        G = D // g
+        res = {}
+        q = torch.randn(H, D, device=device, dtype=torch.float16)
+        o = torch.empty(H, D, device=device, dtype=torch.float16)
+        reps = 5 if H * S >= 1 << 20 else 50
+
+        def put(name, us, nbytes):
+            res[name] = {"us": round(us, 1), "GBps": round(nbytes / us / 1e3, 1),
+                         "frac_of_measured_hbm": round(nbytes / us / 1e3 / peak, 3)}
+
+        k16 = torch.randn(H, S, D, device=device, dtype=torch.float16)
+        v16 = torch.randn(H, S, D, device=device, dtype=torch.float16)
+        for i in range(2):
+            w4.attention_fp16_flash(q.data_ptr(), k16.data_ptr(), v16.data_ptr(), o.data_ptr(), H, S, D)
+        put("fp16", time_graph(torch, lambda i, s: w4.attention_fp16_flash(q.data_ptr(), k16.data_ptr(), v16.data_ptr(),
+                                                                            o.data_ptr(), H, S, D, s), reps),
+            2 * H * S * D * 2)
+        del k16, v16
+        qk = torch.randint(-2**31, 2**31 - 1, (H, S, D // 8), device=device, dtype=torch.int32)
+        qv = torch.randint(-2**31, 2**31 - 1, (H, S, D // 8), device=device, dtype=torch.int32)
+        sk = (torch.rand(H, S, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        sv = (torch.rand(H, S, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        kv = w4.DeviceKVW4(H, S, D, g, G, 1, qk.data_ptr(), sk.data_ptr(), None, qv.data_ptr(), sv.data_ptr(), None)
+        for i in range(2):
+            w4.attention_w4_flash(kv, q.data_ptr(), o.data_ptr())
+        us_c = time_graph(torch, lambda i, s: w4.attention_w4_flash(kv, q.data_ptr(), o.data_ptr(), s), reps)
+        put("w4_gs32", us_c, 2 * H * S * (D // 2 + G * 2))
+        if paged:  # the same bytes read through a shuffled table of 16-token pages
+            page = 16
+            bt = torch.randperm(S // page, device=device).to(torch.int32)
+            for i in range(2):
+                w4.attention_w4_flash_paged(kv, bt.data_ptr(), page, S // page, q.data_ptr(), o.data_ptr())
+            us_p = time_graph(torch, lambda i, s: w4.attention_w4_flash_paged(kv, bt.data_ptr(), page, S // page,
+                                                                              q.data_ptr(), o.data_ptr(), s), reps)
+            put("w4_gs32_paged16", us_p, 2 * H * S * (D // 2 + G * 2))
+            res["w4_gs32_paged16"]["vs_contiguous"] = round(us_c / us_p, 3)
+        del qk, qv
+        bk = torch.randint(0, 0x7E, (H, S, D), device=device, dtype=torch.uint8)
+        bv = torch.randint(0, 0x7E, (H, S, D), device=device, dtype=torch.uint8)
+        f8 = w4.DeviceKVF8(H, S, D, g, G, bk.data_ptr(), sk.data_ptr(), bv.data_ptr(), sv.data_ptr())
+        for i in range(2):
+            w4.attention_f8_flash(f8, q.data_ptr(), o.data_ptr())
+        put("f8_gs32", time_graph(torch, lambda i, s: w4.attention_f8_flash(f8, q.data_ptr(), o.data_ptr(), s), reps),
+            2 * H * S * (D + G * 2))
+        res["shape"] = f"B*H={H} S={S} D={D} gs={g}"
+        out["flash_decode_us"][label] = res
+
+    flash_case(256, 8192, 128, 32, "C4_BH256_S8192", paged=True)
+    flash_case(512, 32768, 128, 32, "C4_BH512_S32768")
+    flash_case(8, 1024, 128, 32, "C4_BH8_S1024_launch_bound")
     assert w4.device_status() == 0
     return out
 
@@ -541,9 +683,11 @@ def cpu_sample(rows):
 
 
 def cpu_baseline(quick):
+    """The reference CPU path on a bounded sample of the headline workload: the host quantizer, dequant_all and the
+    FP64 gemm_oracle as three phases, single-threaded as the reference ships them and row-sliced over all cores."""
     threads = os.cpu_count() or 1
     eng, kind = cpu_engine()
-    rows = 2048 if quick else 2048
+    rows = 2048
     packed, x16, tq = cpu_sample(rows)
     cpu_step(eng, kind, None, rows, threads, packed, x16)  # warm
     reps, t = 0, 0.0
@@ -551,12 +695,25 @@ def cpu_baseline(quick):
         t += cpu_step(eng, kind, None, rows, threads, packed, x16)
         reps += 1
     per = t / reps
+    # single-threaded, phase by phase (the port's entry points: the same algorithm, one thread)
+    from oracle import orc
+    o = orc.Oracle()
+    t0 = time.perf_counter()
+    wd = o.dequant_all_w4(packed)
+    td1 = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    o.gemm_oracle(x16, M_ROWS, K_COLS, wd, rows, threads=1)
+    tg1 = time.perf_counter() - t0
     b = alg_bytes(rows, K_COLS, GS, M_ROWS)
+    scale = N_ROWS / rows
     return {"value": round(b / per / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": kind,
             "sample": f"{rows} of {N_ROWS} rows of the headline GEMM (K={K_COLS}, gs={GS}, M={M_ROWS}); "
-                      f"dequant_all + FP64 gemm_oracle, row-sliced over {threads} threads, {reps} reps; "
-                      f"single-threaded host quantize of the slice took {tq:.2f} s (not in the value)",
-            "us_per_full_gemm_extrapolated": round(per * N_ROWS / rows * 1e6, 1)}
+                      f"value = dequant_all + FP64 gemm_oracle, row-sliced over {threads} threads, {reps} reps",
+            "us_per_full_gemm_extrapolated": round(per * scale * 1e6, 1),
+            "phases_single_thread_ms_full_gemm_extrapolated": {
+                "quantize": round(tq * scale * 1e3, 1), "dequant_all": round(td1 * scale * 1e3, 1),
+                "gemm_oracle_fp64": round(tg1 * scale * 1e3, 1)},
+            "single_thread_value_GBps": round(b / (td1 + tg1) / 1e9, 4)}
 
 
 def run_reference(args):

@@ -141,13 +141,13 @@ int w4b_gemm_w4_hostio(const w4b_packed_w4* p, const void* x_host, void* c_host,
  * For callers that cannot call cudaMalloc: a process whose memory pool has claimed the
  * whole device (the allocation would fail), or a serving loop that forbids allocations
  * (and the implicit device synchronisation of cudaFree) after warm-up. The kernel's
- * scratch lives in a fixed 3.25 MiB array inside the library image, held by every device
+ * scratch lives in a fixed 4.25 MiB array inside the library image, held by every device
  * that loads the library. Serves only shapes of the stream kernel (K % 512 == 0, N >= 64,
  * gs 32/64/128, 16-byte aligned q / scales / x) whose scratch fits: with passes =
- * ceil(M / rows per pass) (16 rows per pass while the activations fit in shared memory
- * beside the ring, fewer for long K), passes * ceil(N/64) * 4 <= 65,536 counters and
- * passes * min(units, SMs) * 8 * (1 or 2) * 512 B <= 3 MiB of fragments (e.g. M <= 16,
- * K <= 4096, N <= 1,000,000); anything else returns W4B_INVALID. The first call on a
+ * ceil(M / 16) and mt = 2 when a pass holds more than 8 rows, passes * ceil(N/64) * 4 <=
+ * 65,536 counters, passes * min(units, SMs) * mt * 4096 B <= 3 MiB of fragments and
+ * passes * (K/512) * (8704 * mt + 256) B <= 1 MiB of arranged activations (e.g. M <= 16,
+ * K <= 28,672, N <= 1,000,000); anything else returns W4B_INVALID. The first call on a
  * device resolves the array's address and clears its counters on the given stream: make
  * it before any stream capture. All calls share the array, which keeps the last call's
  * contents (the kernel re-zeroes the counters it used); calls that overlap on the GPU

@@ -33,9 +33,9 @@ def test_noalloc_matches_regular_entry(oracle, N, K, gs, sym, M):
 
 
 def test_noalloc_rejects_large_k_that_outgrows_the_array(oracle):
-    """K = 8192 with M = 16 halves the rows per pass: N = 1,000,000 then needs more counters than the
-    fixed array holds. Rejected on the host, before any pointer is touched (dummy pointers)."""
-    N, K, gs = 1_000_000, 8192, 128
+    """N = 1,100,000 rows need more per-tile counters than the fixed array holds. Rejected on the host,
+    before any pointer is touched (dummy pointers)."""
+    N, K, gs = 1_100_000, 8192, 128
     desc = w4.DevicePackedW(N, K, gs, K // gs, 1, 256, 256, None)
     with pytest.raises(w4.InvalidArgument):
         w4.gemm_noalloc(desc, 256, 256, 16)
@@ -47,8 +47,8 @@ def test_noalloc_rejects_what_it_cannot_serve(oracle):
     x_d, c_d = dev(oracle.normal_f16(100, 6)), empty_f16(128)
     with pytest.raises(w4.InvalidArgument):
         w4.gemm_noalloc(wts.desc, ptr(x_d), ptr(c_d), 1)
-    big = oracle.quantize_w4(oracle.normal_f64(256 * 256, 7), 256, 256, 128, True)
+    big = oracle.quantize_w4(oracle.normal_f64(256 * 512, 7), 256, 512, 128, True)
     wb = W4Weights(big)
-    xb, cb = dev(oracle.normal_f16(4096 * 256, 8)), empty_f16(4096 * 256)
-    with pytest.raises(w4.InvalidArgument):  # 256 passes of 16 rows: the fragments outgrow the fixed array
-        w4.gemm_noalloc(wb.desc, ptr(xb), ptr(cb), 4096)
+    xb, cb = dev(oracle.normal_f16(16384 * 512, 8)), empty_f16(16384 * 256)
+    with pytest.raises(w4.InvalidArgument):  # 1024 passes of 16 rows: the fragments outgrow the fixed array
+        w4.gemm_noalloc(wb.desc, ptr(xb), ptr(cb), 16384)

@@ -76,6 +76,7 @@ struct DeviceCtx {
   int* status = nullptr;  // device status word written by bounded waits
   Scratch gemm_ws;        // FP32 partial fragments of split panels
   Scratch gemm_counters;  // arrival counters, zero between launches
+  Scratch gemm_xa;        // arranged activations of the stream GEMM's streamed form
   Scratch attn_ws;        // (m, l, acc[D]) partials of split sequences
   Scratch io_x, io_c;     // device staging of the host-buffer entry
 };
@@ -172,14 +173,16 @@ int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint3
   }
   if (kernel == W4B_PATH_STREAM) {
     StreamPlan plan;
-    stream_gemm_plan(N, K, M, ctx->sm_count, &plan);
+    stream_gemm_plan(N, K, M, fmt == 2 ? 0 : gs, ctx->sm_count, &plan);
     CUDA_TRY(ctx->gemm_ws.reserve(plan.ws_bytes, false), "gemm workspace");
     CUDA_TRY(ctx->gemm_counters.reserve(plan.counter_ints * sizeof(int), true), "gemm counters");
+    CUDA_TRY(ctx->gemm_xa.reserve(plan.xa_bytes, false), "gemm activation blocks");
+    int launches = 0;
     CUDA_TRY(stream_gemm_launch(fmt, gs, q, scales, zeros, N, K, G, (const __half*)x, (__half*)c, M,
                                 (__half*)w_out, plan, (float*)ctx->gemm_ws.ptr, (int*)ctx->gemm_counters.ptr,
-                                ctx->status, g_overlap.load() != 0, stream),
+                                ctx->gemm_xa.ptr, ctx->status, g_overlap.load() != 0, stream, &launches),
              who);
-    g_launches += 1;
+    g_launches += (unsigned long long)launches;
     return W4B_OK;
   }
   CUDA_TRY(generic_gemm_launch(fmt, gs, q, scales, zeros, N, K, G, (const __half*)x, (__half*)c, M,

@@ -6,18 +6,19 @@
 // device synchronisation of cudaFree once warm-up is over. The regular entry
 // (w4b_gemm_w4) grows library scratch with cudaMalloc on demand; this one keeps
 // the stream kernel's scratch (the FP32 fragments of panels split between CTAs,
-// their arrival counters and a status word) in a fixed array that is part of the
+// their arrival counters, the arranged activations and a status word) in a fixed array that is part of the
 // library image. Every device that loads the library holds those kNoAllocBytes
 // until the process exits.
 //
 // Limits: only shapes the stream kernel serves (K % 512 == 0, N >= 64, group
 // size 32 / 64 / 128, 16-byte aligned q / scales / x), and only sizes whose
-// scratch fits the array: with passes = ceil(M / rows per pass) (rows per pass is
-// 16 while M * K * 2 bytes of activations fit in shared memory beside the ring,
-// fewer for long K), passes * ceil(N / 64) * 4 counters <= 65,536 and
-// passes * min(units, SMs) * 8 * (1 or 2) * 512 bytes of fragments <= 3 MiB.
-// Anything else is rejected with W4B_INVALID and a message; nothing falls back
-// to an allocating path.
+// scratch fits the array. With passes = ceil(M / 16) and mt = 2 when a pass holds
+// more than 8 rows, else 1:  passes * ceil(N / 64) * 4 counters <= 65,536;
+// passes * min(units, SMs) * mt * 4096 bytes of fragments <= 3 MiB; and, unless
+// M <= 8 rows of K <= ~8K activations stay resident in shared memory,
+// passes * (K / 512) * (8704 * mt + 256) bytes of arranged activations <= 1 MiB
+// (e.g. M <= 16, K <= 28,672, N <= 1,000,000 fits). Anything else is rejected
+// with W4B_INVALID and a message; nothing falls back to an allocating path.
 //
 // The first call on a device resolves the array's device address and clears the
 // counters with a memset on the caller's stream; make that call before any
@@ -38,7 +39,8 @@ namespace {
 constexpr size_t kStatusBytes = 256;
 constexpr size_t kCounterBytes = 256 * 1024;        // 65,536 per-tile arrival counters
 constexpr size_t kFragmentBytes = 3 * 1024 * 1024;  // parked FP32 fragments
-constexpr size_t kNoAllocBytes = kStatusBytes + kCounterBytes + kFragmentBytes;
+constexpr size_t kBlockBytes = 1024 * 1024;         // arranged activations (M > 1 or long K)
+constexpr size_t kNoAllocBytes = kStatusBytes + kCounterBytes + kFragmentBytes + kBlockBytes;
 
 // Host code sees only a stand-in for this symbol: its device address is taken
 // with cudaGetSymbolAddress below, never with the & operator.
@@ -76,12 +78,15 @@ extern "C" int w4b_gemm_w4_noalloc(const w4b_packed_w4* p, const void* x, void* 
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return fail(W4B_CUDA, "gemm noalloc: device attribute query failed");
   StreamPlan plan;
-  stream_gemm_plan(p->N, p->K, M, sms, &plan);
+  stream_gemm_plan(p->N, p->K, M, p->gs, sms, &plan);
   if (plan.ws_bytes > kFragmentBytes)
     return fail(W4B_INVALID, "gemm noalloc: M too large for the fixed scratch (fragments exceed 3 MiB)");
+  if (plan.xa_bytes > kBlockBytes)
+    return fail(W4B_INVALID, "gemm noalloc: M * K too large for the fixed scratch (activation blocks exceed 1 MiB)");
   if (plan.counter_ints * sizeof(int) > kCounterBytes)
     return fail(W4B_INVALID, "gemm noalloc: N * passes too large for the fixed scratch (more than 65,536 tile counters)");
 
+  int launches = 0;
   unsigned char* base = g_base[dev].load(std::memory_order_acquire);
   if (!base) {  // once per device, with that device current
     std::lock_guard<std::mutex> lk(g_mu);
@@ -100,10 +105,10 @@ extern "C" int w4b_gemm_w4_noalloc(const w4b_packed_w4* p, const void* x, void* 
   }
   const cudaError_t e = stream_gemm_launch(
       p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, (const __half*)x, (__half*)c, M,
-      nullptr, plan, (float*)(base + kStatusBytes + kCounterBytes), (int*)(base + kStatusBytes), (int*)base,
-      launch_overlap(), (cudaStream_t)stream);
+      nullptr, plan, (float*)(base + kStatusBytes + kCounterBytes), (int*)(base + kStatusBytes),
+      base + kStatusBytes + kCounterBytes + kFragmentBytes, (int*)base, launch_overlap(), (cudaStream_t)stream, &launches);
   if (e != cudaSuccess) return fail(W4B_CUDA, cudaGetErrorString(e));
-  count_launches(1);
+  count_launches(launches);
   return W4B_OK;
 }
 

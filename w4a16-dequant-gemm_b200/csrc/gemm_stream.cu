@@ -68,10 +68,10 @@ constexpr int SK_KC = 256;                       // k per box (one warp's share 
 constexpr int SK_KU = 2 * SK_KC;                 // k per unit: two boxes side by side
 constexpr int SK_BOX = SK_ROWS * SK_KC / 2;      // 8192 bytes of codes per box
 constexpr int SK_STAGE_Q = 2 * SK_BOX;           // 16384 bytes of codes per unit
-constexpr int SK_META_ROW = 32;                  // <= 16 FP16 scales or 16 E8M0 bytes per row and unit
-constexpr int SK_META_ZOFF = SK_ROWS * SK_META_ROW;  // then 8 bytes of zero words per row
-constexpr int SK_META = SK_META_ZOFF + SK_ROWS * 8;
-constexpr int SK_STAGE = SK_STAGE_Q + SK_META;
+// Scales per row and unit: 512 / gs FP16 values (8, 16 or 32 bytes) or 16 E8M0 bytes; then 8 bytes of zero words.
+__host__ __device__ constexpr int sk_meta_row(int fmt, int gs) { return fmt == 2 ? 16 : 2 * (512 / gs); }
+__host__ __device__ constexpr int sk_meta(int fmt, int gs) { return SK_ROWS * (sk_meta_row(fmt, gs) + 8); }
+__host__ __device__ constexpr int sk_stage(int fmt, int gs) { return SK_STAGE_Q + sk_meta(fmt, gs); }
 constexpr int SK_TILES = 4;                      // 16-row tiles per unit
 constexpr int SK_CONSUMERS = 2 * SK_TILES;       // consumer warps: tile x k half
 constexpr int SK_LOADER = SK_CONSUMERS;          // warp that issues the loads
@@ -81,6 +81,9 @@ constexpr int SK_MAX_STAGES = 12;
 constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 2);  // ring barriers + "parked" + "collected"
 constexpr int SK_RED_BYTES_PER_MT = SK_TILES * 32 * 16;      // the upper k half's fragments, one per tile
 constexpr int SK_COLLECT_BYTES_PER_MT = SK_TILES * 32 * 16;  // other CTAs' fragments, summed
+constexpr int SK_XROW = 1024 + 64;  // streamed activations: bytes per row of a unit's block (== 64 mod 128)
+constexpr int SK_XS_BYTES = 256;    // then the sums of the unit's 4 groups x 16 rows (FP32)
+__host__ __device__ constexpr int sk_xblock(int mt) { return 8 * mt * SK_XROW + SK_XS_BYTES; }
 constexpr int SK_ZERO_BYTES = 512;  // one unit's worth of 16-byte chunks for the four lanes of a column
 constexpr int kSmemOptIn = 232448;  // dynamic shared memory a CTA may ask for (227 KB)
 // With at most this much per CTA two CTAs fit on an SM (228 KB, 1 KB reserved per CTA): the CTA of the next
@@ -113,6 +116,7 @@ struct StreamParams {
   int stages;
   int xrows;    // activation rows per pass (<= 8*MT); pass y covers rows y*xrows ...
   int xpitch;   // bytes between activation rows in shared memory (== 64 mod 128)
+  const uint8_t* xa;  // streamed activations: one arranged block per (pass, unit), written by x_arrange_kernel
   float* ws;
   int* counters;
   int* status;
@@ -320,10 +324,67 @@ constexpr int BAR_HANDED = 1;  // +tile: the upper k half has written its fragme
 constexpr int BAR_TAKEN = 5;   // +tile: the lower half has read it (the upper half waits before rewriting)
 constexpr int BAR_XFILL = 9;   // all consumer warps: the activations are in shared memory
 
-template <int FMT, int GS, int MT, bool HOOK>
+// The word slot of a 256-k box that holds natural word wi (0..31) of an activation row: the chunks the four lanes of
+// a column read together are adjacent.
+//   unfolded: lane c owns words 8c..8c+7, word slot i -> chunk i*4 + c;
+//   folded:   lane c owns words 4c..4c+3 of each 128-k half j, slot (j, i) -> chunk (j*4 + i)*4 + c.
+__device__ __forceinline__ int x_slot(bool fold, int wi) {
+  return fold ? ((wi & 16) | ((wi & 3) << 2) | ((wi >> 2) & 3)) : (((wi & 7) << 2) + (wi >> 3));
+}
+
+// Arranges 8 consecutive activations for the decoder: the pairing (h0,h4,h1,h5,h2,h6,h3,h7); for the folded
+// formats the pairs (h1,h5) and (h3,h7), which meet codes that carry 2^-20 instead of 2^-24, are divided by 16,
+// and *sum8 receives the sum of the 8 values.
+__device__ __forceinline__ uint4 x_arrange8(bool fold, uint4 v, float* sum8) {
+  uint4 pv = pair_permute(v);
+  if (fold) {
+    const __half2 sixteenth = u32_as_h2(0x2C002C00u);
+    pv.y = h2_as_u32(__hmul2_rn(u32_as_h2(pv.y), sixteenth));
+    pv.w = h2_as_u32(__hmul2_rn(u32_as_h2(pv.w), sixteenth));
+    const float2 f0 = __half22float2(u32_as_h2(v.x)), f1 = __half22float2(u32_as_h2(v.y));
+    const float2 f2 = __half22float2(u32_as_h2(v.z)), f3 = __half22float2(u32_as_h2(v.w));
+    *sum8 = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+  }
+  return pv;
+}
+
+// Pre-pass of the streamed-activation form (the counterpart of the reference's x_to_f32_kernel,
+// include/w4/fused.cuh:45-49): writes, for every (pass, 512-k unit), one contiguous block holding the unit's
+// activations of the pass's rows in the arrangement the consumers read (rows padded with zeros to 8 * MT) and,
+// for the folded formats, the FP32 sum of each row over each of the unit's four groups. The GEMM's loader then
+// brings a unit's block in with one bulk copy beside the unit's weights.
+constexpr int XA_THREADS = 64;
+__global__ void __launch_bounds__(XA_THREADS)
+    x_arrange_kernel(const __half* __restrict__ x, uint8_t* __restrict__ xa, int M, int K, int C, int xrows, int mt,
+                     int fold) {
+  pdl_launch_dependents();
+  pdl_wait();  // x may be the previous kernel's output; the blocks may still be read by the previous GEMM
+  const int ch = (int)blockIdx.x, y = (int)blockIdx.y, lane = threadIdx.x & 31;
+  const int m0 = y * xrows, mrows = min(xrows, M - m0), prow = 8 * mt;
+  uint8_t* blk = xa + ((size_t)y * C + ch) * sk_xblock(mt);
+  float* xs = reinterpret_cast<float*>(blk + (size_t)prow * SK_XROW);
+  for (int idx = threadIdx.x; idx < prow * 64; idx += XA_THREADS) {  // (row r, 16-byte chunk widx of the unit)
+    const int r = idx >> 6, widx = idx & 63;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < mrows) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(m0 + r) * K + (size_t)ch * SK_KU) + widx);
+    float xsum = 0.0f;
+    const uint4 pv = x_arrange8(fold != 0, v, &xsum);
+    if (fold) {  // 16 adjacent lanes hold the 16 chunks of one group of one row
+#pragma unroll
+      for (int d = 1; d < 16; d <<= 1) xsum += __shfl_xor_sync(0xffffffffu, xsum, d);
+      if ((lane & 15) == 0) xs[(widx >> 4) * prow + r] = xsum;
+    }
+    const int dst = (widx & 32) + x_slot(fold != 0, widx & 31);
+    *reinterpret_cast<uint4*>(blk + (size_t)r * SK_XROW + ((size_t)dst << 4)) = pv;
+  }
+}
+
+template <int FMT, int GS, int MT, bool HOOK, bool XS>
 __global__ void __launch_bounds__(SK_THREADS, 2)
     stream_gemm_kernel(const __grid_constant__ CUtensorMap tmap, const StreamParams a) {
   constexpr bool FOLD = sk_fold(FMT, GS);
+  constexpr int XBLOCK = sk_xblock(MT);
+  constexpr int SK_META_ROW = sk_meta_row(FMT, GS), SK_META_ZOFF = SK_ROWS * SK_META_ROW, SK_META = sk_meta(FMT, GS);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
   const int stages = a.stages;
@@ -331,11 +392,12 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sm_q = smem;
   uint8_t* sm_meta = sm_q + (size_t)stages * SK_STAGE_Q;
+  // activations: streamed form - one arranged block per stage; resident form - the pass's rows, a zero area for
+  // absent rows and, for the folded formats, the sum of row m over group gidx at [gidx][8 * MT] (FP32)
   uint8_t* sm_x = sm_meta + (size_t)stages * SK_META;
-  uint8_t* sm_zero = sm_x + (size_t)a.xrows * a.xpitch;  // SK_ZERO_BYTES of zeros: the "activations" of absent rows
-  // folded formats: sum of the activations of row m over group gidx, at [gidx][8 * MT] (FP32)
-  float* sm_xs = reinterpret_cast<float*>(sm_zero + SK_ZERO_BYTES);
-  uint8_t* sm_red = reinterpret_cast<uint8_t*>(sm_xs) + (FOLD ? (size_t)(a.K >> 7) * 8 * MT * 4 : 0);
+  uint8_t* sm_zero = sm_x + (XS ? (size_t)stages * XBLOCK : (size_t)a.xrows * a.xpitch);
+  float* sm_xs = reinterpret_cast<float*>(sm_zero + (XS ? 0 : SK_ZERO_BYTES));
+  uint8_t* sm_red = reinterpret_cast<uint8_t*>(sm_xs) + ((FOLD && !XS) ? (size_t)(a.K >> 7) * 8 * MT * 4 : 0);
   uint8_t* sm_collect = sm_red + MT * SK_RED_BYTES_PER_MT;
   const uint32_t sm_bar = smem_u32(sm_collect + MT * SK_COLLECT_BYTES_PER_MT);
   auto full_bar = [&](int s) { return sm_bar + 8u * (uint32_t)s; };
@@ -376,28 +438,26 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
 
   if (wid == SK_LOADER) {
     // ------------------------------ loader ------------------------------
-    // Reads nothing but the packed weights, so it never waits for the previous grid.
+    // The weights are read without waiting for the previous grid; in the streamed form the activation blocks,
+    // which the arrange kernel before this grid writes, follow once that kernel has completed.
     constexpr int NGU = FMT == F_MX ? SK_KU / 32 : SK_KU / GS;  // scales per row and unit
     constexpr int SBYTES = FMT == F_MX ? NGU : 2 * NGU;        // 8 (gs 128), 16 (gs 64, MX) or 32 (gs 32) bytes
     constexpr int ZBYTES = NGU > 8 ? 8 : 4;                    // zero words of the unit's groups
-    Cursor cur;
-    cur.start(walk, C);
-    int s = 0;
-    uint32_t ph = 0;
-    for (int j = 0; j < total; ++j) {
-      if (!mbar_wait(empty_bar(s), ph ^ 1u, a.status, ST_STREAM_EMPTY_TIMEOUT)) return;
+    // One unit's weights: two boxes + the rows' scales / zero words; the stage's full barrier then expects the
+    // boxes' bytes (and, in the streamed form, the activation block's, which issue_x brings).
+    auto issue_w = [&](int s, int p, int ch) {
       if (lane == 0) {
         const uint32_t dst = smem_u32(sm_q) + (uint32_t)s * SK_STAGE_Q;
-        mbar_arrive_expect_tx(full_bar(s), SK_STAGE_Q);
-        tma_load_2d(dst, &tmap, cur.ch * (SK_KU / 8), cur.p * SK_ROWS, full_bar(s));
-        tma_load_2d(dst + SK_BOX, &tmap, cur.ch * (SK_KU / 8) + SK_KC / 8, cur.p * SK_ROWS, full_bar(s));
+        mbar_arrive_expect_tx(full_bar(s), SK_STAGE_Q + (XS ? XBLOCK : 0));
+        tma_load_2d(dst, &tmap, ch * (SK_KU / 8), p * SK_ROWS, full_bar(s));
+        tma_load_2d(dst + SK_BOX, &tmap, ch * (SK_KU / 8) + SK_KC / 8, p * SK_ROWS, full_bar(s));
       }
       const uint32_t meta = smem_u32(sm_meta) + (uint32_t)s * SK_META;
-      const int g0 = cur.ch * NGU;  // the unit's first group (or MX block) within the row
+      const int g0 = ch * NGU;  // the unit's first group (or MX block) within the row
 #pragma unroll
       for (int rr = 0; rr < SK_ROWS / 32; ++rr) {
         const int row = lane + 32 * rr;
-        const int n = min(cur.p * SK_ROWS + row, a.N - 1);  // rows past N: any valid row, never used
+        const int n = min(p * SK_ROWS + row, a.N - 1);  // rows past N: any valid row, never used
         const uint8_t* src = (const uint8_t*)a.scales + ((size_t)n * a.G + g0) * (FMT == F_MX ? 1 : 2);
         if constexpr (SBYTES == 32) {
           cp_async<16>(meta + row * SK_META_ROW, src);
@@ -409,6 +469,36 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
           cp_async<ZBYTES>(meta + SK_META_ZOFF + row * 8, a.zeros + (size_t)n * a.wG + (size_t)((g0 >> 3) & ~(ZBYTES / 4 - 1)));
       }
       cp_async_arrive_noinc(full_bar(s));
+    };
+    // The unit's arranged activations (streamed form): one bulk copy of the (pass, unit) block.
+    auto issue_x = [&](int s, int ch) {
+      if (XS && lane == 0)
+        bulk_load_1d(smem_u32(sm_x) + (uint32_t)s * XBLOCK, a.xa + ((size_t)blockIdx.y * C + ch) * XBLOCK, XBLOCK,
+                     full_bar(s));
+    };
+    Cursor cur;
+    cur.start(walk, C);
+    // The first ring fill needs no free-stage wait. Weights go out at once; the activation blocks are written by
+    // the arrange kernel that precedes this grid, so they follow once that kernel has completed.
+    const int first = min(stages, total);
+    Cursor cx = cur;
+    for (int j = 0; j < first; ++j) {
+      issue_w(j, cur.p, cur.ch);
+      cur.next(walk, C);
+    }
+    if (XS) {
+      pdl_wait();
+      for (int j = 0; j < first; ++j) {
+        issue_x(j, cx.ch);
+        cx.next(walk, C);
+      }
+    }
+    int s = first == stages ? 0 : first;
+    uint32_t ph = first == stages ? 1u : 0u;
+    for (int j = first; j < total; ++j) {
+      if (!mbar_wait(empty_bar(s), ph ^ 1u, a.status, ST_STREAM_EMPTY_TIMEOUT)) return;
+      issue_w(s, cur.p, cur.ch);
+      issue_x(s, cur.ch);
       if (++s == stages) {
         s = 0;
         ph ^= 1u;
@@ -504,6 +594,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
   const uint32_t sw1 = FOLD ? ((uint32_t)(c + 4) ^ (uint32_t)rg) << 4 : ((uint32_t)(2 * c + 1) ^ (uint32_t)rg) << 4;
 
   pdl_wait();  // the activations may be the previous grid's output
+  if constexpr (!XS) {
   // Activations of this pass: rows m0 .. m0+mrows-1, FP16, each row re-ordered so that the 16 bytes a lane
   // needs for one packed word are one chunk in the decoder's pairing (h0,h4,h1,h5,h2,h6,h3,h7), and the chunks
   // the four lanes of a column read together are adjacent:
@@ -549,6 +640,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
     if (tid < SK_ZERO_BYTES / 16) reinterpret_cast<uint4*>(sm_zero)[tid] = make_uint4(0u, 0u, 0u, 0u);
     named_barrier(BAR_XFILL, 32 * SK_CONSUMERS);
   }
+  }
 
   // x rows this lane supplies as B-fragment column g (and g + 8 for the second m-tile). Lanes whose
   // column has no activation row read the zero area instead (plain loads that the compiler is free to
@@ -557,8 +649,13 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
   bool xok[MT];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
-    xok[mt] = (g + 8 * mt) < mrows;
-    xrow[mt] = (xok[mt] ? sm_x + (size_t)(g + 8 * mt) * a.xpitch : sm_zero) + (c << 4);
+    if (XS) {  // the stage's block holds 8 * MT rows (absent ones as zeros); this warp reads its k half
+      xok[mt] = false;
+      xrow[mt] = sm_x + (size_t)(g + 8 * mt) * SK_XROW + (kh << 9) + (c << 4);
+    } else {
+      xok[mt] = (g + 8 * mt) < mrows;
+      xrow[mt] = (xok[mt] ? sm_x + (size_t)(g + 8 * mt) * a.xpitch : sm_zero) + (c << 4);
+    }
   }
   const W4Consts kc = w4_consts();
   int s = 0;        // ring slot of the next unit
@@ -598,7 +695,8 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
         const uint4 qb1 = *reinterpret_cast<const uint4*>(qs + 8 * 128 + sw1);
         const uint8_t* xu[MT];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) xu[mt] = xrow[mt] + (xok[mt] ? ((size_t)ch << 9) : 0);  // 32 chunks of 16 bytes per unit
+        for (int mt = 0; mt < MT; ++mt)  // resident: 32 chunks of 16 bytes per 256 k of the row; streamed: the stage's block
+          xu[mt] = xrow[mt] + (XS ? (size_t)s_now * XBLOCK : (xok[mt] ? ((size_t)ch << 9) : 0));
         if constexpr (FOLD) {
           // the unit holds 4 groups per row (8 bytes of scales, one zero word); this warp's half has two
           const uint32_t sa2 = *reinterpret_cast<const uint32_t*>(meta + ra * SK_META_ROW + 4 * kh);
@@ -663,7 +761,9 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
             const float fzb = __uint_as_float(0x4B000000u | ((zzb >> (4 * j)) & 0xFu)) - 8388608.0f;
             const float sa24 = sa * 16777216.0f, sb24 = sb * 16777216.0f;
             const float nza = -(sa * fza), nzb = -(sb * fzb);
-            const float* xs = sm_xs + (size_t)(2 * ch + j) * (8 * MT) + 2 * c;
+            const float* xs = XS ? reinterpret_cast<const float*>(sm_x + (size_t)s_now * XBLOCK + 8 * MT * SK_XROW) +
+                                       (2 * kh + j) * (8 * MT) + 2 * c
+                                 : sm_xs + (size_t)(2 * ch + j) * (8 * MT) + 2 * c;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
               const float2 xs2 = *reinterpret_cast<const float2*>(xs + 8 * mt);
@@ -809,10 +909,10 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-template <int FMT, int GS, int MT, bool HOOK>
+template <int FMT, int GS, int MT, bool HOOK, bool XS>
 cudaError_t launch_one(const CUtensorMap& tmap, const StreamParams& sp, dim3 grid, size_t smem, bool overlap,
                        cudaStream_t stream) {
-  auto kern = stream_gemm_kernel<FMT, GS, MT, HOOK>;
+  auto kern = stream_gemm_kernel<FMT, GS, MT, HOOK, XS>;
   // The shared-memory opt-in is a per-device attribute of the function: set it once on every device used.
   static std::atomic<bool> configured[kMaxDevices];
   int dev = 0;
@@ -837,30 +937,44 @@ cudaError_t launch_one(const CUtensorMap& tmap, const StreamParams& sp, dim3 gri
   return cudaLaunchKernelEx(&cfg, kern, tmap, sp);
 }
 
+template <int FMT, int GS, bool XS>
+cudaError_t launch_mt(const CUtensorMap& tmap, const StreamParams& sp, int mt, dim3 grid, size_t smem,
+                      bool overlap, cudaStream_t stream) {
+  const bool hook = sp.w_out != nullptr;
+  if (mt == 1)
+    return hook ? launch_one<FMT, GS, 1, true, XS>(tmap, sp, grid, smem, overlap, stream)
+                : launch_one<FMT, GS, 1, false, XS>(tmap, sp, grid, smem, overlap, stream);
+  return hook ? launch_one<FMT, GS, 2, true, XS>(tmap, sp, grid, smem, overlap, stream)
+              : launch_one<FMT, GS, 2, false, XS>(tmap, sp, grid, smem, overlap, stream);
+}
+
 template <int FMT, int GS>
 cudaError_t launch_fmt(const CUtensorMap& tmap, const StreamParams& sp, int mt, dim3 grid, size_t smem,
                        bool overlap, cudaStream_t stream) {
-  const bool hook = sp.w_out != nullptr;
-  if (mt == 1)
-    return hook ? launch_one<FMT, GS, 1, true>(tmap, sp, grid, smem, overlap, stream)
-                : launch_one<FMT, GS, 1, false>(tmap, sp, grid, smem, overlap, stream);
-  return hook ? launch_one<FMT, GS, 2, true>(tmap, sp, grid, smem, overlap, stream)
-              : launch_one<FMT, GS, 2, false>(tmap, sp, grid, smem, overlap, stream);
+  return sp.xa ? launch_mt<FMT, GS, true>(tmap, sp, mt, grid, smem, overlap, stream)
+               : launch_mt<FMT, GS, false>(tmap, sp, mt, grid, smem, overlap, stream);
 }
 
-// Shared memory of one CTA without the ring: alignment slack, barriers, `rows` activation rows, zero area,
-// exchange areas.
+// Shared memory of one CTA without the ring, resident form: alignment slack, barriers, `rows` activation rows,
+// zero area, group sums (folded formats), exchange areas.
 size_t fixed_smem(int rows, int K) {
   const int mt = rows > 8 ? 2 : 1;
   return 1024 + SK_BAR_BYTES + (size_t)rows * (K * 2 + 64) + SK_ZERO_BYTES + (size_t)(K / 128) * 8 * mt * 4 +
          (size_t)mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT);
 }
-// Ring depth that fits beside `rows` activation rows within `budget` bytes per CTA.
-constexpr int kMinStages = 3;      // one box being consumed, two in flight
+// Ring depth that fits beside `rows` resident activation rows within `budget` bytes per CTA.
+constexpr int kMinStages = 3;      // one unit being consumed, two in flight
 constexpr int kMinStagesHalf = 5;  // a ring worth confining to half an SM
-int stages_for(int rows, int K, int budget = kSmemOptIn) {
+int stages_for(int rows, int K, int stage_bytes, int budget) {
   const long long room = (long long)budget - (long long)fixed_smem(rows, K);
-  return room <= 0 ? 0 : (int)(room / SK_STAGE);
+  return room <= 0 ? 0 : (int)(room / stage_bytes);
+}
+// Streamed form: the activations travel with the units, a stage also holds the unit's arranged block.
+size_t fixed_smem_xs(int mt) {
+  return 1024 + SK_BAR_BYTES + (size_t)mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT);
+}
+int stages_for_xs(int mt, int stage_bytes, int budget) {
+  return (int)(((long long)budget - (long long)fixed_smem_xs(mt)) / (stage_bytes + sk_xblock(mt)));
 }
 
 }  // namespace
@@ -871,32 +985,52 @@ bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, cons
   if (gs_or_0_for_mx != 0 && gs_or_0_for_mx != 32 && gs_or_0_for_mx != 64 && gs_or_0_for_mx != 128)
     return false;
   if (((uintptr_t)q | (uintptr_t)scales | (uintptr_t)x) & 15u) return false;
-  if (K > 65536 || stages_for(1, K) < kMinStages) return false;  // one activation row must fit beside the shortest ring
+  if (K > (1 << 20)) return false;
   // 32-bit unit arithmetic: units * CTAs below 2^31 (>= 100 GB of packed weights on 148 SMs)
   if ((long long)((N + SK_ROWS - 1) / SK_ROWS) * (K / SK_KU) * 1024 >= (1LL << 31)) return false;
   return encode_tiled() != nullptr;
 }
 
-void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan) {
+void stream_gemm_plan(int N, int K, int M, int gs_or_0_for_mx, int sm_count, StreamPlan* plan) {
   const int xpitch = K * 2 + 64;
-  // activation rows per pass: 16 if they leave room for the shortest ring, else 8, else fewer
-  int rows = M < 16 ? M : 16;
-  if (rows > 8 && stages_for(rows, K) < kMinStages) rows = 8;
-  while (rows > 1 && stages_for(rows, K) < kMinStages) --rows;
-  plan->rows_per_pass = rows;
-  plan->mt = rows > 8 ? 2 : 1;
-  plan->passes = (M + rows - 1) / rows;
-  // Half an SM's shared memory when a useful ring fits in it (so that the next launch's CTA can sit beside
-  // this one), else all of it.
-  int st = stages_for(rows, K, kSmemHalf);
-  if (st < kMinStagesHalf) st = stages_for(rows, K);
-  plan->stages = st > SK_MAX_STAGES ? SK_MAX_STAGES : st;
+  const int stage = gs_or_0_for_mx == 0 ? sk_stage(F_MX, 32) : sk_stage(F_W4_SYM, gs_or_0_for_mx);
   plan->P = (N + SK_ROWS - 1) / SK_ROWS;
   plan->C = K / SK_KU;
   plan->U = (long long)plan->P * plan->C;
   plan->grid_x = (int)(plan->U < sm_count ? plan->U : sm_count);
   plan->xpitch = xpitch;
-  plan->smem = fixed_smem(rows, K) + (size_t)plan->stages * SK_STAGE;
+  // Resident form: the activation rows stay in shared memory, re-arranged once per CTA. It is used while they
+  // are small (about 36 KB: one row of up to ~16K activations, four rows of 4K): staging them costs every CTA a
+  // pass over all of them, and they take room from the ring. One row that leaves a ring of kMinStagesHalf
+  // stages in half an SM's shared memory keeps to that half, so that the next launch's CTA sits beside this one.
+  if (M <= 8 && (size_t)M * xpitch <= 36 * 1024) {
+    plan->streamed = 0;
+    plan->rows_per_pass = M;
+    plan->mt = 1;
+    plan->passes = 1;
+    int st = stages_for(M, K, stage, kSmemHalf);
+    if (st < kMinStagesHalf) st = stages_for(M, K, stage, kSmemOptIn);
+    plan->stages = st > SK_MAX_STAGES ? SK_MAX_STAGES : st;
+    plan->smem = fixed_smem(M, K) + (size_t)plan->stages * stage;
+    plan->xa_bytes = 0;
+  } else {
+    // Streamed form: a pre-pass arranges the activations per 512-k unit and the loader brings each unit's block
+    // in beside its weights, so shared memory does not grow with K and up to 16 rows go through in one pass.
+    const int rows = M < 16 ? M : 16;
+    plan->streamed = 1;
+    plan->rows_per_pass = rows;
+    plan->mt = rows > 8 ? 2 : 1;
+    plan->passes = (M + rows - 1) / rows;
+    // Measured on B200 (N = 14336, K = 4096, M = 8 / 16, launches overlapped): rings of 4 / 3 stages are as fast
+    // as deeper ones (12.4 / 17.7 us), and two consecutive launches sharing an SM cost 4 us (the arrange kernel
+    // sits between them in the stream) - so the request is kept above half an SM's shared memory.
+    const int st = stages_for_xs(plan->mt, stage, kSmemOptIn);
+    const int want = plan->mt == 1 ? 5 : 4;
+    plan->stages = st > want ? want : st;
+    plan->smem = fixed_smem_xs(plan->mt) + (size_t)plan->stages * (stage + sk_xblock(plan->mt));
+    if (plan->smem <= (size_t)kSmemHalf) plan->smem = (size_t)kSmemHalf + 1024;
+    plan->xa_bytes = (size_t)plan->passes * plan->C * sk_xblock(plan->mt);
+  }
   plan->ws_bytes = (size_t)plan->passes * plan->grid_x * 2 * SK_TILES * plan->mt * 32 * sizeof(float4);
   plan->counter_ints = (size_t)plan->passes * plan->P * SK_TILES;
 }
@@ -907,11 +1041,12 @@ void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan) {
 // serialization: the grid may start while the previous kernel of the stream is still running
 // and reads the packed weights (q / scales / zeros) before that kernel has completed - the
 // caller promises that the previous kernel does not write them. Activations, outputs and
-// scratch are only touched after the previous kernel has completed.
+// scratch are only touched after the previous kernel has completed. `xa` (plan.xa_bytes, 16-byte aligned) holds
+// the arranged activations of the streamed form; it is written by a pre-pass launched here.
 cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
                                int N, int K, int G, const __half* x, __half* c, int M, __half* w_out,
-                               const StreamPlan& plan, float* ws, int* counters, int* status, bool overlap,
-                               cudaStream_t stream) {
+                               const StreamPlan& plan, float* ws, int* counters, void* xa, int* status,
+                               bool overlap, cudaStream_t stream, int* launches) {
   CUtensorMap tmap;
   const cuuint64_t gdim[2] = {(cuuint64_t)(K / 8), (cuuint64_t)N};
   const cuuint64_t gstride[1] = {(cuuint64_t)(K / 8) * 4};
@@ -943,6 +1078,22 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   sp.counters = counters;
   sp.status = status;
   sp.xrows = plan.rows_per_pass;
+  sp.xa = plan.streamed ? (const uint8_t*)xa : nullptr;
+  if (launches) *launches = plan.streamed ? 2 : 1;
+  if (plan.streamed) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)plan.C, (unsigned)plan.passes);
+    cfg.blockDim = dim3(XA_THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, x_arrange_kernel, x, (uint8_t*)xa, M, K, plan.C, plan.rows_per_pass,
+                                             plan.mt, (int)sk_fold(fmt, gs));
+    if (e != cudaSuccess) return e;
+  }
   const dim3 grid((unsigned)plan.grid_x, (unsigned)plan.passes);  // pass y = activation rows y*rows_per_pass ...
   switch (fmt) {
     case F_W4_SYM:

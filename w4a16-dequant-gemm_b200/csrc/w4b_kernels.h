@@ -39,25 +39,27 @@ cudaError_t generic_gemm_launch(int fmt, int gs, const uint32_t* q, const void* 
 
 // ---- gemm_stream.cu ---------------------------------------------------------
 struct StreamPlan {
-  int rows_per_pass;  // activation rows resident in shared memory per pass
+  int streamed;       // 1: activations arranged by a pre-pass and streamed with the units; 0: resident in shared memory
+  int rows_per_pass;  // activation rows per pass
   int mt;             // 8-row m-tiles per pass (1 or 2)
   int passes;         // grid.y
   int stages;         // ring depth
-  int P, C;           // panels of 128 rows, chunks of 256 k
+  int P, C;           // panels of 64 rows, units of 512 k per panel
   long long U;        // work units
   int grid_x;         // persistent CTAs
   int xpitch;
   size_t smem;
+  size_t xa_bytes;      // arranged activations of the streamed form (0 in the resident form)
   size_t ws_bytes;      // FP32 partial-fragment slots
   size_t counter_ints;  // per-(pass, tile) arrival counters, zero between launches
 };
 bool stream_gemm_supported(int N, int K, int gs_or_0_for_mx, const void* q, const void* scales,
                            const void* x);
-void stream_gemm_plan(int N, int K, int M, int sm_count, StreamPlan* plan);
+void stream_gemm_plan(int N, int K, int M, int gs_or_0_for_mx, int sm_count, StreamPlan* plan);
 cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
                                int N, int K, int G, const __half* x, __half* c, int M, __half* w_out,
-                               const StreamPlan& plan, float* ws, int* counters, int* status, bool overlap,
-                               cudaStream_t stream);
+                               const StreamPlan& plan, float* ws, int* counters, void* xa, int* status,
+                               bool overlap, cudaStream_t stream, int* launches);
 
 // ---- gemm_tensor.cu ---------------------------------------------------------
 bool tensor_gemm_supported(int N, int K, const void* q, const void* x);
