@@ -77,6 +77,7 @@ struct DeviceCtx {
   Scratch gemm_ws;        // FP32 partial fragments of split panels
   Scratch gemm_counters;  // arrival counters, zero between launches
   Scratch gemm_xa;        // arranged activations of the stream GEMM's streamed form
+  Scratch tensor_counters;  // per-tile arrival counters of the tensor GEMM's split-K form, zero between launches
   Scratch attn_ws;        // (m, l, acc[D]) partials of split sequences
   Scratch io_x, io_c;     // device staging of the host-buffer entry
 };
@@ -165,8 +166,12 @@ int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint3
   if (int rc = get_ctx(&ctx)) return rc;
   const int kernel = route_kernel(entry, N, K, fmt == 2 ? 0 : gs, q, scales, x, w_out);
   if (kernel == W4B_PATH_TENSOR) {
+    TensorPlan tplan;
+    tensor_gemm_plan(N, K, M, ctx->sm_count, &tplan);
+    CUDA_TRY(ctx->gemm_ws.reserve(tplan.ws_bytes, false), "gemm workspace");
+    CUDA_TRY(ctx->tensor_counters.reserve(tplan.counter_ints * sizeof(int), true), "gemm counters");
     CUDA_TRY(tensor_gemm_launch(fmt, gs, q, scales, zeros, N, K, G, (const __half*)x, (__half*)c, M, (__half*)w_out,
-                                ctx->status, stream),
+                                tplan, (float*)ctx->gemm_ws.ptr, (int*)ctx->tensor_counters.ptr, ctx->status, stream),
              who);
     g_launches += 1;
     return W4B_OK;
@@ -233,6 +238,7 @@ int w4b_device_status(void) {
     // shares a panel between CTAs would take stale fragments for fresh ones.
     cudaMemset(ctx->status, 0, sizeof(int));
     if (ctx->gemm_counters.ptr) cudaMemset(ctx->gemm_counters.ptr, 0, ctx->gemm_counters.cap);
+    if (ctx->tensor_counters.ptr) cudaMemset(ctx->tensor_counters.ptr, 0, ctx->tensor_counters.cap);
     if (na_status) {
       cudaMemset(na_status, 0, sizeof(int));
       cudaMemset(na_counters, 0, na_bytes);

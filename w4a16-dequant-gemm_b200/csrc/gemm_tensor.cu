@@ -25,11 +25,18 @@
 //                       convert to FP16 and store c[m*N + n] (a warp writes 32
 //                       consecutive n).
 //
+// When the tiles alone would leave most SMs idle (N of a few thousand), the K range of a tile is split between
+// several CTAs (grid.z): each writes its FP32 partial tile to a workspace, bumps the tile's counter, and the CTA
+// that arrives last adds the partials in split order - fixed, so the output is bit-identical from run to run -
+// and stores FP16.
+//
 // Shapes served: K % 32 == 0 (16-byte row pitch of q and x), 16-byte aligned q / x,
 // any N, any M (grid.y tiles M by 256), any group size the format allows. The K
 // tail (K % 64 != 0) is zero-filled by TMA on both operands.
 // Every wait is bounded; a kernel that gives up still frees its TMEM.
 #include <cuda.h>
+
+#include <atomic>
 
 #include "w4b_common.cuh"
 #include "w4b_kernels.h"
@@ -58,6 +65,9 @@ struct TensorParams {
   int mtile;   // activation rows per CTA (<= 256)
   int stages;
   uint32_t tx_bytes;  // bytes the two TMA boxes of a chunk deliver (boxes are clipped to N and M)
+  int splits;         // CTAs that share a tile's K range (grid.z)
+  float* ws;          // splits > 1: partial tiles [tile][split][column][128 rows]
+  int* counters;      // splits > 1: one arrival counter per tile, zero between launches
   int* status;
 };
 
@@ -126,10 +136,14 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
   auto stage_free = [&](int s) { return sm_bar + 8u * (uint32_t)(2 * TK_MAX_STAGES + s); };
   const uint32_t acc_ready = sm_bar + 8u * (uint32_t)(3 * TK_MAX_STAGES);
   const uint32_t tmem_slot = acc_ready + 8u;  // where tcgen05.alloc writes the TMEM base address
+  const uint32_t last_slot = tmem_slot + 4u;  // split-K: whether this CTA arrived last at its tile's counter
 
   const int n0 = (int)blockIdx.x * TK_ROWS;
   const int m0 = (int)blockIdx.y * a.mtile;
-  const int nchunks = (a.K + TK_KC - 1) / TK_KC;
+  // this CTA's chunks: an equal share of the tile's K range
+  const int all_chunks = (a.K + TK_KC - 1) / TK_KC;
+  const int kc_begin = (int)((long long)all_chunks * blockIdx.z / a.splits);
+  const int nchunks = (int)((long long)all_chunks * (blockIdx.z + 1) / a.splits) - kc_begin;
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -165,8 +179,8 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
       for (int kc = 0; kc < nchunks; ++kc) {
         if (!mbar_wait(stage_free(s), ph ^ 1u, a.status, ST_TENSOR_TIMEOUT)) break;
         mbar_arrive_expect_tx(load_full(s), a.tx_bytes);
-        tma_load_2d(q_tile(s), &tmap_q, kc * (TK_KC / 8), n0, load_full(s));
-        tma_load_2d(x_tile(s), &tmap_x, kc * TK_KC, m0, load_full(s));
+        tma_load_2d(q_tile(s), &tmap_q, (kc_begin + kc) * (TK_KC / 8), n0, load_full(s));
+        tma_load_2d(x_tile(s), &tmap_x, (kc_begin + kc) * TK_KC, m0, load_full(s));
         if (++s == stages) {
           s = 0;
           ph ^= 1u;
@@ -213,7 +227,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
     // the two groups of a chunk are fetched one chunk ahead, outside the wait for the codes.
     const int gshift = FMT == 2 ? 5 : a.gshift;
     const bool pow2 = gshift >= 5;
-    auto group_of = [&](int kc, int h) { return min((kc * TK_KC + 32 * h) >> gshift, a.G - 1); };
+    auto group_of = [&](int kc, int h) { return min(((kc_begin + kc) * TK_KC + 32 * h) >> gshift, a.G - 1); };
     auto fetch_w4 = [&](int grp) {
       const __half sc = ((const __half*)a.scales)[(size_t)n * a.G + grp];
       const uint32_t z = FMT == 0 ? 8u : ((a.zeros[(size_t)n * wG + (grp >> 3)] >> (4 * (grp & 7))) & 0xFu);
@@ -248,7 +262,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
       const MxBlock mcur[2] = {mx_block(ecur[0]), mx_block(ecur[1])};
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
-        const int k0 = kc * TK_KC + 8 * w;
+        const int k0 = (kc_begin + kc) * TK_KC + 8 * w;
         __half2 o[4];
         if (FMT == 2) {
           dq_mx_word(cw[w], mcur[w >> 2], o);
@@ -279,13 +293,44 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
       for (int cb = 16 * hf; cb < a.mpad; cb += 16 * TK_GROUPS) {
         uint32_t v[16];
         tmem_ld16(tmem_acc + lane_base + (uint32_t)cb, v);
-        if (n0 + r < a.N) {
+        if (a.splits > 1) {  // FP32 partial of this split: [tile][split][column][row], a warp writes 32 rows
+          float* part = a.ws + ((((size_t)blockIdx.y * gridDim.x + blockIdx.x) * a.splits + blockIdx.z) * a.mpad + cb) * TK_ROWS + r;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) __stcg(part + (size_t)i * TK_ROWS, __uint_as_float(v[i]));
+        } else if (n0 + r < a.N) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int m = m0 + cb + i;
             if (cb + i < a.mtile && m < a.M) a.c[(size_t)m * a.N + n0 + r] = __float2half_rn(__uint_as_float(v[i]));
           }
         }
+      }
+    }
+  }
+  if (a.splits > 1) {
+    // The split that arrives last at the tile's counter adds all partials in split order and stores the tile.
+    __threadfence();  // this CTA's partial is visible before its arrival is counted
+    __syncthreads();
+    int* cnt = a.counters + (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+    if (tid == 0) {
+      const int prev = atomicAdd(cnt, 1);
+      const uint32_t last = prev == a.splits - 1 ? 1u : 0u;
+      if (last) *cnt = 0;  // ready for the next launch
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(last_slot), "r"(last) : "memory");
+    }
+    __syncthreads();
+    uint32_t is_last;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(is_last) : "r"(last_slot) : "memory");
+    if (is_last && wid < TK_DECODERS) {
+      __threadfence();
+      const float* base = a.ws + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * a.splits) * (size_t)a.mpad * TK_ROWS;
+      const int r = tid & (TK_ROWS - 1);
+      for (int col = tid >> 7; col < a.mtile; col += TK_DECODERS / 4) {
+        const int m = m0 + col;
+        if (m >= a.M) break;
+        float sum = 0.0f;
+        for (int sp = 0; sp < a.splits; ++sp) sum += __ldcg(base + ((size_t)sp * a.mpad + col) * TK_ROWS + r);
+        if (n0 + r < a.N) a.c[(size_t)m * a.N + n0 + r] = __float2half_rn(sum);
       }
     }
   }
@@ -318,17 +363,39 @@ template <int FMT, bool HOOK>
 cudaError_t launch_one(const CUtensorMap& tq, const CUtensorMap& tx, const TensorParams& tp, dim3 grid, size_t smem,
                        cudaStream_t stream) {
   auto kern = tensor_gemm_kernel<FMT, HOOK>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+  // The shared-memory opt-in is a per-device attribute of the function: set it once on every device used.
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev].store(true, std::memory_order_release);
   }
   kern<<<grid, TK_THREADS, smem, stream>>>(tq, tx, tp);
   return cudaGetLastError();
 }
 
 }  // namespace
+
+// CTAs per tile along K: 1 when the tiles fill at least half the SMs, else enough to fill them, with at least
+// 8 chunks (512 k) per CTA.
+void tensor_gemm_plan(int N, int K, int M, int sm_count, TensorPlan* plan) {
+  const int mtile = M < 256 ? M : 256, mpad = (mtile + 15) / 16 * 16;
+  const long long tiles = (long long)((N + TK_ROWS - 1) / TK_ROWS) * ((M + mtile - 1) / mtile);
+  const int chunks = (K + TK_KC - 1) / TK_KC;
+  int splits = 1;
+  if (tiles * 2 <= sm_count) {
+    splits = (int)(sm_count / tiles);
+    if (splits > chunks / 8) splits = chunks / 8;
+    if (splits < 1) splits = 1;
+  }
+  plan->splits = splits;
+  plan->ws_bytes = splits > 1 ? (size_t)tiles * splits * mpad * TK_ROWS * sizeof(float) : 0;
+  plan->counter_ints = splits > 1 ? (size_t)tiles : 0;
+}
 
 bool tensor_gemm_supported(int N, int K, const void* q, const void* x) {
   if (N < 1 || K < 32 || K % 32 != 0) return false;
@@ -337,9 +404,12 @@ bool tensor_gemm_supported(int N, int K, const void* q, const void* x) {
 }
 
 cudaError_t tensor_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros, int N,
-                               int K, int G, const __half* x, __half* c, int M, __half* w_out, int* status,
-                               cudaStream_t stream) {
+                               int K, int G, const __half* x, __half* c, int M, __half* w_out, const TensorPlan& plan,
+                               float* ws, int* counters, int* status, cudaStream_t stream) {
   TensorParams tp;
+  tp.splits = plan.splits;
+  tp.ws = ws;
+  tp.counters = counters;
   tp.q = q;
   tp.scales = scales;
   tp.zeros = zeros;
@@ -390,7 +460,8 @@ cudaError_t tensor_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cudaErrorInvalidValue;
   }
-  const dim3 grid((unsigned)((N + TK_ROWS - 1) / TK_ROWS), (unsigned)((M + tp.mtile - 1) / tp.mtile));
+  const dim3 grid((unsigned)((N + TK_ROWS - 1) / TK_ROWS), (unsigned)((M + tp.mtile - 1) / tp.mtile),
+                  (unsigned)plan.splits);
   const bool hook = w_out != nullptr;
   if (fmt == 0)
     return hook ? launch_one<0, true>(tq, tx, tp, grid, smem, stream) : launch_one<0, false>(tq, tx, tp, grid, smem, stream);

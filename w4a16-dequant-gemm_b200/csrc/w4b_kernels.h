@@ -62,10 +62,17 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
                                bool overlap, cudaStream_t stream, int* launches);
 
 // ---- gemm_tensor.cu ---------------------------------------------------------
+struct TensorPlan {
+  int splits;           // CTAs that share a tile's K range
+  size_t ws_bytes;      // FP32 partial tiles (0 when splits == 1)
+  size_t counter_ints;  // per-tile arrival counters, zero between launches
+};
+void tensor_gemm_plan(int N, int K, int M, int sm_count, TensorPlan* plan);
 bool tensor_gemm_supported(int N, int K, const void* q, const void* x);
+// The caller has sized ws / counters by the plan; counters are all zero between launches.
 cudaError_t tensor_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros, int N,
-                               int K, int G, const __half* x, __half* c, int M, __half* w_out, int* status,
-                               cudaStream_t stream);
+                               int K, int G, const __half* x, __half* c, int M, __half* w_out, const TensorPlan& plan,
+                               float* ws, int* counters, int* status, cudaStream_t stream);
 
 // ---- attn_flash.cu ----------------------------------------------------------
 enum : int { ATTN_FP16 = 0, ATTN_W4_SYM = 1, ATTN_W4_ASYM = 2, ATTN_F8 = 3 };
