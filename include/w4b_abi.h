@@ -181,6 +181,21 @@ int w4b_attn_flash_f8(const w4b_kv_f8* p, const void* q, void* out, void* stream
  * ceil(S/page) int32 entries on the device; hooks write in logical order. */
 int w4b_attn_flash_w4_paged(const w4b_kv_w4* p, const int* bt, int page, int npages, const void* q,
                             void* out, void* stream, void* k_out, void* v_out);
+/* Batched form of the paged entry; it has no counterpart in the reference, whose
+ * attention_w4_flash_paged (include/w4/kvflash.cuh:725-764) takes one sequence (one
+ * block table) per call. nseq sequences share one pool: sequence i has seq_lens[i]
+ * positions (device array, 1 <= seq_lens[i] <= max_seq_len; max_seq_len is a host
+ * value that sizes the launch) and the block table bt + i * bt_stride (device,
+ * bt_stride >= ceil(max_seq_len / page)); q and out are [nseq][H][D]. One slice pass
+ * and one combine serve all sequences, and every sequence is cut exactly as a
+ * single-sequence call of its length would be: out[i] is bit-identical to
+ * w4b_attn_flash_w4_paged on sequence i. p->S is ignored. Served for D = 64 / 128,
+ * gs = 32 / 64 / 128 and 16-byte aligned caches and q; other shapes return
+ * W4B_INVALID (call the per-sequence entry). seq_lens and bt contents are not
+ * validated. */
+int w4b_attn_flash_w4_paged_batched(const w4b_kv_w4* p, const int* bt, int bt_stride, const int* seq_lens,
+                                    int nseq, int max_seq_len, int page, int npages, const void* q,
+                                    void* out, void* stream);
 /* attention_fp16 / attention_w4 (include/w4/kvattention.cuh:226-248): the
  * legacy single-block entries; same results contract, and they keep the
  * reference's S <= 4096 and D <= 512 rejections. */

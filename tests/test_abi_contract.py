@@ -176,3 +176,22 @@ def test_f8_rejections():
                  (4, ONE, ONE, 4, 66, 8), (1, ONE, ONE, 4, 64, 32), (4, ONE, ONE, 1 << 24, 512, 32)]:
         with pytest.raises(w4.InvalidArgument):
             w4.dequant_f8(*args)
+
+
+def test_batched_paged_contract():
+    """The batched paged entry rejects malformed calls before touching any pointer (dummy pointers)."""
+    kv = w4.DeviceKVW4(2, 64, 128, 32, 4, 1, ONE * 16, ONE * 16, None, ONE * 16, ONE * 16, None)
+
+    def call(desc=kv, bt=ONE * 16, stride=8, lens=ONE * 16, nseq=2, smax=100, page=16, npages=16, q=ONE * 16,
+             out=ONE * 16):
+        w4.attention_w4_flash_paged_batched(desc, bt, stride, lens, nseq, smax, page, npages, q, out)
+
+    bad = w4.InvalidArgument
+    for kw in (dict(bt=None), dict(lens=None), dict(nseq=0), dict(smax=0), dict(page=0), dict(npages=0),
+               dict(npages=6),      # 6 pages of 16 rows cannot hold 100 positions
+               dict(stride=6),      # the longest sequence needs 7 table entries
+               dict(q=None), dict(out=None),
+               dict(desc=w4.DeviceKVW4(2, 64, 96, 32, 3, 1, ONE * 16, ONE * 16, None, ONE * 16, ONE * 16, None)),  # D = 96
+               dict(desc=w4.DeviceKVW4(2, 64, 128, 32, 4, 0, ONE * 16, ONE * 16, None, ONE * 16, ONE * 16, None))):  # asym, no zeros
+        with pytest.raises(bad):
+            call(**kw)

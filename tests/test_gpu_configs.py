@@ -226,6 +226,60 @@ def test_c5_paged_geometry_two_sequences(oracle):
         assert cases.rel_l2(cases.f16(bits(out_p)), ref) <= TOL
 
 
+def test_batched_paged_matches_per_sequence_calls(oracle):
+    """The batched paged entry: sequences of different lengths over one pool (two of them share prefix pages),
+    one launch; every sequence's output must carry the bits of the per-sequence entry, which is checked
+    against the FP64 reference."""
+    H, D, gs, page = 4, 128, 32, 16
+    lens = [4608, 300, 4100, 16, 1]
+    rng = np.random.default_rng(21)
+    Smax = max(lens)
+    k, v = rng.standard_normal((H, Smax, D)), rng.standard_normal((H, Smax, D))
+    c = oracle.quantize_cache_w4(k.ravel(), v.ravel(), H, Smax, D, gs, True)  # per position: prefixes agree
+    lp = (Smax + page - 1) // page
+    npages = lp + 7
+    perm = np.random.default_rng(22).permutation(npages).astype(np.int32)
+    bt_long = perm[:lp]
+    # the pool: the long sequence's pages scattered by its table (more pages than it needs)
+    wd, G = (D + 7) // 8, c["G"]
+    rows = npages * page
+    pool = {}
+    for n, w in (("q_k", wd), ("q_v", wd), ("s_k", G), ("s_v", G)):
+        a = np.zeros((H, rows, w), dtype=c[n].dtype)
+        src = np.zeros((H, lp * page, w), dtype=c[n].dtype)
+        src[:, :Smax] = c[n].reshape(H, Smax, w)
+        for i, phys in enumerate(bt_long):
+            a[:, phys * page:(phys + 1) * page] = src[:, i * page:(i + 1) * page]
+        pool[n] = a
+    t = {n: dev(np.ascontiguousarray(pool[n]).ravel()) for n in ("q_k", "q_v", "s_k", "s_v")}
+    # every sequence is a prefix of the long one: its table is the head of the long table
+    nseq, stride = len(lens), lp + 3
+    bt = np.zeros((nseq, stride), dtype=np.int32)
+    for i, L in enumerate(lens):
+        n_i = (L + page - 1) // page
+        bt[i, :n_i] = bt_long[:n_i]
+    qs = oracle.normal_f16(nseq * H * D, 23)
+    q_d, bt_d, lens_d = dev(qs), dev(bt.ravel()), dev(np.array(lens, dtype=np.int32))
+    desc = w4.DeviceKVW4(H, Smax, D, gs, G, 1, ptr(t["q_k"]), ptr(t["s_k"]), None, ptr(t["q_v"]), ptr(t["s_v"]), None)
+    out_b = empty_f16(nseq * H * D)
+    out_b.fill_(float("nan"))
+    w4.attention_w4_flash_paged_batched(desc, ptr(bt_d), stride, ptr(lens_d), nseq, Smax, page, npages, ptr(q_d),
+                                        ptr(out_b))
+    sync_ok()
+    got = bits(out_b).reshape(nseq, H * D)
+    kd = oracle.dequant_cache_w4(c, "k").reshape(H, Smax, D)
+    vd = oracle.dequant_cache_w4(c, "v").reshape(H, Smax, D)
+    for i, L in enumerate(lens):
+        d_i = w4.DeviceKVW4(H, L, D, gs, G, 1, ptr(t["q_k"]), ptr(t["s_k"]), None, ptr(t["q_v"]), ptr(t["s_v"]), None)
+        out_1 = empty_f16(H * D)
+        w4.attention_w4_flash_paged(d_i, ptr(bt_d) + 4 * i * stride, page, npages, ptr(q_d) + 2 * i * H * D, ptr(out_1))
+        sync_ok()
+        assert np.array_equal(bits(out_1), got[i]), f"sequence {i} (length {L})"
+        ref = oracle.attention_reference(qs[i * H * D:(i + 1) * H * D], np.ascontiguousarray(kd[:, :L]).ravel(),
+                                         np.ascontiguousarray(vd[:, :L]).ravel(), H, L, D)
+        assert cases.rel_l2(cases.f16(got[i]), ref) <= TOL, f"sequence {i}"
+
+
 def test_peer_allgather_loopback():
     """The exchange kernels on one GPU: two arenas stand for two ranks, the pushes of a step are launched one
     after the other on one stream (a push only waits for the OTHER rank's previous step, which an earlier

@@ -70,6 +70,7 @@ ABI = {
     "w4b_attn_flash_w4": (_I, [C.POINTER(_KvW4), _P, _P, _P, _P, _P]),
     "w4b_attn_flash_f8": (_I, [C.POINTER(_KvF8), _P, _P, _P, _P, _P]),
     "w4b_attn_flash_w4_paged": (_I, [C.POINTER(_KvW4), _P, _I, _I, _P, _P, _P, _P, _P]),
+    "w4b_attn_flash_w4_paged_batched": (_I, [C.POINTER(_KvW4), _P, _I, _P, _I, _I, _I, _I, _P, _P, _P]),
     "w4b_attn_single_fp16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "w4b_attn_single_w4": (_I, [C.POINTER(_KvW4), _P, _P, _P, _P, _P]),
     "w4b_peer_alloc": (_I, [C.c_size_t, C.POINTER(_P), _P]),
@@ -244,6 +245,14 @@ def attention_f8_flash(p: DeviceKVF8, q, out, stream=None, k_out=None, v_out=Non
 def attention_w4_flash_paged(p: DeviceKVW4, bt, page, npages, q, out, stream=None, k_out=None,
                              v_out=None):  # kvflash.cuh:725
     _check(lib.w4b_attn_flash_w4_paged(C.byref(p._c()), bt, page, npages, q, out, stream, k_out, v_out))
+
+
+def attention_w4_flash_paged_batched(p: DeviceKVW4, bt, bt_stride, seq_lens, nseq, max_seq_len, page, npages, q, out,
+                                     stream=None):
+    """nseq sequences over one pool in one launch (no reference counterpart: its paged entry takes one
+    sequence per call); out[i] carries the bits of attention_w4_flash_paged on sequence i."""
+    _check(lib.w4b_attn_flash_w4_paged_batched(C.byref(p._c()), bt, bt_stride, seq_lens, nseq, max_seq_len, page, npages,
+                                               q, out, stream))
 
 
 def attention_fp16(q, k16, v16, out, H, S, D, stream=None):  # kvattention.cuh:226

@@ -502,6 +502,44 @@ int w4b_attn_flash_w4_paged(const w4b_kv_w4* p, const int* bt, int page, int npa
   return run_attn(s, q, out, p->H, p->S, p->D, (cudaStream_t)stream, k_out, v_out, "kv paged flash");
 }
 
+int w4b_attn_flash_w4_paged_batched(const w4b_kv_w4* p, const int* bt, int bt_stride, const int* seq_lens, int nseq,
+                                    int max_seq_len, int page, int npages, const void* q, void* out, void* stream) {
+  // the per-sequence contract of w4b_attn_flash_w4_paged (kvflash.cuh:733-754) with p->S ignored
+  if (!p) INVALID("kv paged batched: null descriptor");
+  if (p->H < 1 || p->D < 1) INVALID("kv paged batched: bad dims");
+  if (nseq < 1 || max_seq_len < 1) INVALID("kv paged batched: bad sequence count or length");
+  if (p->D > kKvMaxD) INVALID("kv paged batched: D exceeds the shared bound");
+  if (p->gs < 8 || p->gs % 8 != 0) INVALID("kv paged batched: gs must be a multiple of 8");
+  if (p->G != (p->D + p->gs - 1) / p->gs) INVALID("kv paged batched: G inconsistent with D, gs");
+  if (!p->q_k || !p->s_k || !p->q_v || !p->s_v || !bt || !seq_lens) INVALID("kv paged batched: null pointer");
+  if (!p->symmetric && (!p->z_k || !p->z_v)) INVALID("kv paged batched: asymmetric without zeros");
+  if (p->symmetric && (p->z_k || p->z_v)) INVALID("kv paged batched: symmetric carries zeros");
+  if (page < 1 || npages < 1 || (unsigned long long)npages * (unsigned long long)page < (unsigned long long)max_seq_len)
+    INVALID("kv paged batched: bad page geometry");
+  if ((long long)npages * page >= (1LL << 31)) INVALID("kv paged batched: pool rows exceed 2^31");
+  if (max_seq_len > 65535 * kFlashTile) INVALID("kv paged batched: sequence exceeds tile-grid bound");
+  if (bt_stride < (max_seq_len + page - 1) / page) INVALID("kv paged batched: block-table rows shorter than the longest sequence");
+  if ((long long)nseq * p->H > INT_MAX) INVALID("kv paged batched: too many (sequence, head) rows");
+  if (!q || !out) INVALID("kv paged batched: null io");
+  AttnSource s = w4_source(p);
+  s.bt = bt;
+  s.page = page;
+  s.slab_rows = (long long)npages * page;
+  if (!attn_mma_supported(s, p->D, q, nullptr, nullptr))
+    INVALID("kv paged batched: served for D = 64 / 128, gs = 32 / 64 / 128 and 16-byte aligned caches and q; "
+            "call w4b_attn_flash_w4_paged per sequence otherwise");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  const int max_splits = attn_flash_splits(p->H, max_seq_len, ctx->sm_count);
+  CUDA_TRY(ctx->attn_ws.reserve(attn_flash_ws_bytes(nseq * p->H, p->D, max_splits), false), "attention workspace");
+  int launches = 0;
+  CUDA_TRY(attn_flash_batched_launch(s, (const __half*)q, (__half*)out, p->H, p->D, nseq, seq_lens, bt_stride, max_splits,
+                                     ctx->sm_count, (float*)ctx->attn_ws.ptr, (cudaStream_t)stream, &launches),
+           "kv paged batched");
+  g_launches += (unsigned long long)launches;
+  return W4B_OK;
+}
+
 // ---- all-gather over peer memory (no reference counterpart) --------------------------------
 
 int w4b_peer_alloc(size_t bytes, void** ptr, void* handle64) {

@@ -243,10 +243,15 @@ __global__ void __launch_bounds__(FA_THREADS) flash_decode_kernel(const FlashPar
   }
 }
 
-// Per head: rescale and add the split partials in split order.
-__global__ void flash_combine_kernel(const float* __restrict__ ws, __half* __restrict__ out, int splits, int D) {
+// Per head: rescale and add the split partials in split order. Batched form (seq_lens != null): row h of the
+// output belongs to sequence h / H, whose slice count follows from its own length; the workspace keeps
+// `splits` (the longest sequence's count) slots per row.
+__global__ void flash_combine_kernel(const float* __restrict__ ws, __half* __restrict__ out, int splits, int D,
+                                     const int* __restrict__ seq_lens, int H, int sm_count) {
   const int h = blockIdx.x;
   const float* hb = ws + (size_t)h * splits * (size_t)(D + 2);
+  if (seq_lens) splits = attn_flash_splits(H, __ldg(seq_lens + h / H), sm_count);
+  if (splits == 1 && seq_lens) return;  // the slice pass wrote the output itself
   float mx = -CUDART_INF_F;
   for (int s = 0; s < splits; ++s) mx = fmaxf(mx, hb[(size_t)s * (D + 2)]);
   float den = 0.0f;
@@ -283,22 +288,6 @@ cudaError_t launch_fmt(const FlashParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-int attn_flash_splits(int H, int S, int sm_count) {
-  // About eight waves of CTAs at four resident CTAs per SM (a partial last wave then costs
-  // little), but slices as long as possible - 256 positions (four steps per warp), else 128, else
-  // FA_MIN_SPLIT - as long as that still gives every SM two CTAs.
-  long long want = (32LL * sm_count + H - 1) / H;
-  long long cap = 1;
-  for (int slice = 256; slice >= FA_MIN_SPLIT; slice >>= 1) {
-    cap = (S + slice - 1) / slice;
-    if (cap * H >= 2LL * sm_count) break;
-  }
-  if (want > cap) want = cap;
-  if (want > 65535) want = 65535;
-  if (want < 1) want = 1;
-  return (int)want;
-}
-
 size_t attn_flash_ws_bytes(int H, int D, int splits) {
   return (size_t)H * splits * (size_t)(D + 2) * sizeof(float);
 }
@@ -325,7 +314,7 @@ cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* ou
     e = attn_mma_launch(src, q, out, H, S, D, splits, ws, k_out, v_out, stream);
     *launches = 1;
     if (e != cudaSuccess || splits == 1) return e;
-    flash_combine_kernel<<<H, 128, 0, stream>>>(ws, out, splits, D);
+    flash_combine_kernel<<<H, 128, 0, stream>>>(ws, out, splits, D, nullptr, 0, 0);
     *launches = 2;
     return cudaGetLastError();
   }
@@ -337,7 +326,21 @@ cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* ou
   }
   *launches = 1;
   if (e != cudaSuccess || splits == 1) return e;
-  flash_combine_kernel<<<H, 128, 0, stream>>>(ws, out, splits, D);
+  flash_combine_kernel<<<H, 128, 0, stream>>>(ws, out, splits, D, nullptr, 0, 0);
+  *launches = 2;
+  return cudaGetLastError();
+}
+
+// Batched paged decode attention: nseq sequences over one pool, one slice pass and one combine for all of them.
+// Every sequence is cut exactly as a single-sequence call of its length would be, so its output carries the same
+// bits. `max_splits` = attn_flash_splits(H, longest sequence, sm_count); ws holds nseq * H * max_splits partials.
+cudaError_t attn_flash_batched_launch(const AttnSource& src, const __half* q, __half* out, int H, int D, int nseq,
+                                      const int* seq_lens, int bt_stride, int max_splits, int sm_count, float* ws,
+                                      cudaStream_t stream, int* launches) {
+  cudaError_t e = attn_mma_batched_launch(src, q, out, H, D, nseq, seq_lens, bt_stride, max_splits, sm_count, ws, stream);
+  *launches = 1;
+  if (e != cudaSuccess || max_splits == 1) return e;
+  flash_combine_kernel<<<nseq * H, 128, 0, stream>>>(ws, out, max_splits, D, seq_lens, H, sm_count);
   *launches = 2;
   return cudaGetLastError();
 }

@@ -47,12 +47,14 @@ struct MmaParams {
   int H, S, splits;
   int gshift;  // log2(group size)
   int wide;    // the hooks may be written 16 bytes at a time
+  // batched paged form: grid.x = nseq * H; sequence i has seq_lens[i] positions and the block table
+  // bt + i * bt_stride; its slices are those of a single-sequence call of that length
+  int nseq;             // 0: single sequence
+  const int* seq_lens;  // device, nseq entries
+  int bt_stride;
+  int sm_count;
+  int pshift;  // log2(page) when the page is a power of two >= 16, else -1
 };
-
-// Row of logical position t inside its head's slab.
-__device__ __forceinline__ int row_of(const AttnSource& s, int t) {
-  return s.bt ? s.bt[t / s.page] * s.page + (t % s.page) : t;
-}
 
 // The arrays of one head (rows are then indexed with 32-bit multiplies by constant strides).
 struct HeadBase {
@@ -229,13 +231,18 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   constexpr int NT = EV / 2;  // output tiles (16 d each... per lane: rows g and g+8)
   __shared__ float sm_ml[MA_WARPS][2];
   __shared__ float sm_acc[MA_WARPS][D];
-  const int h = blockIdx.x, sp = blockIdx.y;
+  const int hx = blockIdx.x, sp = blockIdx.y;  // hx: row of q / out (sequence-major in the batched form)
+  const int h = p.nseq ? hx % p.H : hx;        // head: selects the slab
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
+  const int S = p.nseq ? __ldg(p.seq_lens + hx / p.H) : p.S;
+  const int splits = p.nseq ? attn_flash_splits(p.H, S, p.sm_count) : p.splits;
+  if (sp >= splits) return;  // (batched: the grid is sized for the longest sequence)
+  const int* bt = p.src.bt ? p.src.bt + (p.nseq ? (size_t)(hx / p.H) * p.bt_stride : 0) : nullptr;
   // slices are cut at multiples of 64 positions: the four warps of a CTA get the same number of blocks
-  const int units = (p.S + MA_WARPS * MA_BLOCK - 1) / (MA_WARPS * MA_BLOCK);
-  const int t0 = MA_WARPS * MA_BLOCK * (int)((long long)units * sp / p.splits);
-  const int t1 = min(p.S, MA_WARPS * MA_BLOCK * (int)((long long)units * (sp + 1) / p.splits));
+  const int units = (S + MA_WARPS * MA_BLOCK - 1) / (MA_WARPS * MA_BLOCK);
+  const int t0 = MA_WARPS * MA_BLOCK * (int)((long long)units * sp / splits);
+  const int t1 = min(S, MA_WARPS * MA_BLOCK * (int)((long long)units * (sp + 1) / splits));
   const float scale = rsqrtf((float)D);
   const AttnSource& s = p.src;
   HeadBase hb;
@@ -256,7 +263,7 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   uint4 qf[NQ];
 #pragma unroll
   for (int i = 0; i < NQ; ++i) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q + (size_t)h * D + E * c) + i);
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q + (size_t)hx * D + E * c) + i);
     qf[i] = (FMT == ATTN_W4_SYM || FMT == ATTN_W4_ASYM) ? pair_permute(v) : v;
   }
 
@@ -271,12 +278,26 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   auto fetch = [&](BlockData<FMT, D>& blk, int tb) {
     const int last = t1 - 1;  // positions past the slice read a valid row and get weight 0
     int rk[2], rv[4];
-    rk[0] = row_of(s, min(tb + g, last));
-    rk[1] = row_of(s, min(tb + g + 8, last));
-    rv[0] = row_of(s, min(tb + 2 * c, last));
-    rv[1] = row_of(s, min(tb + 2 * c + 1, last));
-    rv[2] = row_of(s, min(tb + 2 * c + 8, last));
-    rv[3] = row_of(s, min(tb + 2 * c + 9, last));
+    if (bt == nullptr || p.pshift >= 0) {
+      // contiguous cache, or pages that are a power of two >= 16: the block's 16 positions (tb is a multiple of
+      // 16) lie in one page, so one table entry serves the block
+      const int base = bt == nullptr ? tb : (__ldg(bt + (tb >> p.pshift)) << p.pshift) + (tb & ((1 << p.pshift) - 1));
+      const int lim = last - tb;
+      rk[0] = base + min(g, lim);
+      rk[1] = base + min(g + 8, lim);
+      rv[0] = base + min(2 * c, lim);
+      rv[1] = base + min(2 * c + 1, lim);
+      rv[2] = base + min(2 * c + 8, lim);
+      rv[3] = base + min(2 * c + 9, lim);
+    } else {
+      auto row = [&](int t) { return __ldg(bt + t / s.page) * s.page + (t % s.page); };
+      rk[0] = row(min(tb + g, last));
+      rk[1] = row(min(tb + g + 8, last));
+      rv[0] = row(min(tb + 2 * c, last));
+      rv[1] = row(min(tb + 2 * c + 1, last));
+      rv[2] = row(min(tb + 2 * c + 8, last));
+      rv[3] = row(min(tb + 2 * c + 9, last));
+    }
     blk.load(hb, rk, rv, g, c, p.gshift);
   };
 
@@ -496,10 +517,10 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       a = a * fa + a2 * fb;
       mm = mn;
     }
-    if (p.splits == 1) {
-      p.out[(size_t)h * D + d] = __float2half_rn(a / ll);
+    if (splits == 1) {
+      p.out[(size_t)hx * D + d] = __float2half_rn(a / ll);
     } else {
-      float* part = p.ws + ((size_t)h * p.splits + sp) * (size_t)(D + 2);
+      float* part = p.ws + ((size_t)hx * (p.nseq ? p.splits : splits) + sp) * (size_t)(D + 2);
       if (d == 0) {
         part[0] = mm;
         part[1] = ll;
@@ -511,7 +532,7 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
 
 template <int FMT, int D>
 cudaError_t launch_d(const MmaParams& p, cudaStream_t stream) {
-  const dim3 grid((unsigned)p.H, (unsigned)p.splits);
+  const dim3 grid((unsigned)(p.nseq ? p.nseq * p.H : p.H), (unsigned)p.splits);
   if (p.k_out || p.v_out)
     attn_mma_kernel<FMT, D, true><<<grid, MA_THREADS, 0, stream>>>(p);
   else
@@ -540,6 +561,26 @@ bool attn_mma_supported(const AttnSource& src, int D, const void* q, const void*
 
 // One pass over the cache: partial (m, l, acc) per (head, split) into ws, or the output itself
 // when splits == 1. The caller runs the split combine.
+static int page_shift(const AttnSource& src) {
+  if (!src.bt) return -1;
+  for (int b = 4; b < 31; ++b)
+    if (src.page == (1 << b)) return b;
+  return -1;
+}
+
+static cudaError_t launch_any(MmaParams& p, int D, cudaStream_t stream) {
+  const AttnSource& src = p.src;
+  p.gshift = src.gs == 128 ? 7 : (src.gs == 64 ? 6 : 5);
+  p.wide = ((((uintptr_t)p.k_out | (uintptr_t)p.v_out) & 15u) == 0) ? 1 : 0;
+  p.pshift = page_shift(src);
+  switch (src.fmt) {
+    case ATTN_FP16: return launch_fmt<ATTN_FP16>(p, D, stream);
+    case ATTN_W4_SYM: return launch_fmt<ATTN_W4_SYM>(p, D, stream);
+    case ATTN_W4_ASYM: return launch_fmt<ATTN_W4_ASYM>(p, D, stream);
+    default: return launch_fmt<ATTN_F8>(p, D, stream);
+  }
+}
+
 cudaError_t attn_mma_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
                             float* ws, __half* k_out, __half* v_out, cudaStream_t stream) {
   MmaParams p;
@@ -552,14 +593,32 @@ cudaError_t attn_mma_launch(const AttnSource& src, const __half* q, __half* out,
   p.H = H;
   p.S = S;
   p.splits = splits;
-  p.gshift = src.gs == 128 ? 7 : (src.gs == 64 ? 6 : 5);
-  p.wide = ((((uintptr_t)k_out | (uintptr_t)v_out) & 15u) == 0) ? 1 : 0;
-  switch (src.fmt) {
-    case ATTN_FP16: return launch_fmt<ATTN_FP16>(p, D, stream);
-    case ATTN_W4_SYM: return launch_fmt<ATTN_W4_SYM>(p, D, stream);
-    case ATTN_W4_ASYM: return launch_fmt<ATTN_W4_ASYM>(p, D, stream);
-    default: return launch_fmt<ATTN_F8>(p, D, stream);
-  }
+  p.nseq = 0;
+  p.seq_lens = nullptr;
+  p.bt_stride = 0;
+  p.sm_count = 0;
+  return launch_any(p, D, stream);
+}
+
+// The batched paged form: grid.x = nseq * H rows of q / out, grid.y = the longest sequence's slice count.
+cudaError_t attn_mma_batched_launch(const AttnSource& src, const __half* q, __half* out, int H, int D, int nseq,
+                                    const int* seq_lens, int bt_stride, int max_splits, int sm_count, float* ws,
+                                    cudaStream_t stream) {
+  MmaParams p;
+  p.src = src;
+  p.q = q;
+  p.out = out;
+  p.ws = ws;
+  p.k_out = nullptr;
+  p.v_out = nullptr;
+  p.H = H;
+  p.S = 0;
+  p.splits = max_splits;
+  p.nseq = nseq;
+  p.seq_lens = seq_lens;
+  p.bt_stride = bt_stride;
+  p.sm_count = sm_count;
+  return launch_any(p, D, stream);
 }
 
 }  // namespace w4b

@@ -91,10 +91,29 @@ struct AttnSource {
   int page;
   long long slab_rows;
 };
-int attn_flash_splits(int H, int S, int sm_count);
+// Slices per head of the split-S pass (the same on the host and, for the batched form, on the device).
+__host__ __device__ inline int attn_flash_splits(int H, int S, int sm_count) {
+  // About eight waves of CTAs at four resident CTAs per SM (a partial last wave then costs
+  // little), but slices as long as possible - 256 positions (four steps per warp), else 128, else
+  // 64 - as long as that still gives every SM two CTAs.
+  long long want = (32LL * sm_count + H - 1) / H;
+  long long cap = 1;
+  for (int slice = 256; slice >= 64; slice >>= 1) {
+    cap = (S + slice - 1) / slice;
+    if (cap * H >= 2LL * sm_count) break;
+  }
+  if (want > cap) want = cap;
+  if (want > 65535) want = 65535;
+  if (want < 1) want = 1;
+  return (int)want;
+}
 size_t attn_flash_ws_bytes(int H, int D, int splits);
 cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
                               float* ws, __half* k_out, __half* v_out, cudaStream_t stream, int* launches);
+
+cudaError_t attn_flash_batched_launch(const AttnSource& src, const __half* q, __half* out, int H, int D, int nseq,
+                                      const int* seq_lens, int bt_stride, int max_splits, int sm_count, float* ws,
+                                      cudaStream_t stream, int* launches);
 
 // ---- attn_mma.cu ------------------------------------------------------------
 // The tensor-pipe form of the flash pass for D = 64 / 128 and group sizes 32 / 64 / 128;
@@ -102,6 +121,10 @@ cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* ou
 bool attn_mma_supported(const AttnSource& src, int D, const void* q, const void* k_out, const void* v_out);
 cudaError_t attn_mma_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
                             float* ws, __half* k_out, __half* v_out, cudaStream_t stream);
+
+cudaError_t attn_mma_batched_launch(const AttnSource& src, const __half* q, __half* out, int H, int D, int nseq,
+                                    const int* seq_lens, int bt_stride, int max_splits, int sm_count, float* ws,
+                                    cudaStream_t stream);
 
 // ---- peer_gather.cu ---------------------------------------------------------
 constexpr int kMaxPeers = 8;
