@@ -274,8 +274,9 @@ def run_mine(args):
             dist.all_gather_into_tensor(gathered.view(-1), c.view(-1))
         else:
             buf = i % w4.peer.NBUF  # slice buffers in rotation
-            w4.gemm(packs[i % copies][3], x.data_ptr(), pg.slot(buf, rank), M, st)
-            pg.push(buf, st)  # (waits for the peers' previous slices only; pg.wait() completes a sequence)
+            # one kernel: the GEMM's epilogue stores the slice into every peer's arena and posts the step
+            # (it waits for the peers' previous slices only; pg.wait() completes a sequence)
+            pg.gemm_push(packs[i % copies][3], x.data_ptr(), M, buf, st)
 
     class _Arena:  # a window of device memory as a torch tensor of int16
         def __init__(self, ptr, n):
@@ -335,7 +336,7 @@ def run_mine(args):
             raise SystemExit(f"bench: a bounded device wait ran out (status {int(bad.item())})")
 
     # The K steps are captured once in a CUDA graph, so the timed region holds device work only. At
-    # N > 1 a step is the GEMM plus the peer all-gather kernel; no NCCL call is in the graph.
+    # N > 1 a step is still one kernel (the GEMM stores its slice into the peers' arenas); no NCCL call is in the graph.
     launches_before = w4.launch_count()
     use_graph = world == 1 or peer_mode
     if use_graph:
@@ -439,9 +440,9 @@ def run_mine(args):
                                      "touched only after the previous kernel has completed)",
                    "timing": "one CUDA graph of K launches, CUDA events" if world == 1 else
                              "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks" if not peer_mode else
-                             "one CUDA graph of K steps (GEMM + peer all-gather kernel; a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
+                             "one CUDA graph of K steps (one kernel per step: the GEMM, whose epilogue stores its output slice into every peer's arena over NVLink and posts the step; a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
                    "parallelism": "single GPU" if world == 1 else
-                                  f"column-parallel N x{world} + all-gather over NVLink peer stores" if peer_mode else
+                                  f"column-parallel N x{world}, all-gather by peer stores from the GEMM's epilogue" if peer_mode else
                                   f"column-parallel N x{world} + NCCL all-gather",
                    "rel_l2_vs_fp32_product": rel},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",

@@ -206,7 +206,7 @@ int w4b_attn_single_w4(const w4b_kv_w4* p, const void* q, void* out, void* strea
 
 /* ---- all-gather of the sharded GEMM's output over NVLink peer memory ----- */
 
-/* These six entries have no counterpart in the reference (it is single-GPU). They
+/* These seven entries have no counterpart in the reference (it is single-GPU). They
  * are the exchange step of the column-parallel GEMM: one process per GPU, every
  * rank owns an arena that its peers map through CUDA IPC, and one launch per step
  * stores this rank's output slice into every peer's arena with plain peer stores
@@ -235,6 +235,18 @@ int w4b_allgather_push(const void* src, size_t bytes, void* const* dst, void* co
                        const void* flags_local, void* counters, int rank, int world, int wait_now,
                        void* stream);
 int w4b_allgather_wait(const void* flags_local, const void* counters, int rank, int world, void* stream);
+/* The sharded GEMM and its exchange in ONE kernel (no reference counterpart): w4b_gemm_w4 through the
+ * stream kernel (M <= 16, a shape that kernel serves) whose epilogue stores every output element to c
+ * (this rank's slice buffer in its own arena) and to c_peer[p], the same buffer in rank p's arena, with
+ * plain peer stores; the grid's last warp then posts the step to flag_dst[p] exactly as
+ * w4b_allgather_push does (same flags, same counters: the two entries can be mixed, and
+ * w4b_allgather_wait completes a sequence). Before its first peer store the kernel waits (bounded) for the
+ * peers' slices of the previous step, so ranks stay within one step of each other; rotate over three slice
+ * buffers. done: a zero-initialised 32-bit word in this rank's arena. c_peer, flag_dst are HOST arrays of
+ * device pointers (entries [rank] ignored). */
+int w4b_gemm_w4_push(const w4b_packed_w4* p, const void* x, void* c, int M, void* const* c_peer,
+                     void* const* flag_dst, const void* flags_local, void* counters, void* done, int rank,
+                     int world, void* stream);
 
 #ifdef __cplusplus
 }

@@ -321,6 +321,53 @@ def test_peer_allgather_loopback():
             assert int(flags[o]) == step
 
 
+def test_gemm_push_loopback(oracle):
+    """The GEMM whose epilogue does the exchange, on one GPU: two arenas stand for two ranks that each own half
+    of W's rows; a step launches rank 0's GEMM and then rank 1's on one stream (each only waits for the other's
+    PREVIOUS step), then both wait. Afterwards every arena must hold both slices, equal to the plain GEMM's
+    output bit for bit, over more steps than there are slice buffers."""
+    N, K, gs, M, world = 1024, 1024, 128, 4, 2
+    p = oracle.quantize_w4(oracle.normal_f64(N * K, 51) * 0.02, N, K, gs, False)
+    wts = W4Weights(p)
+    shards = [w4.shard.shard_w4(wts.desc, world, r) for r in range(world)]
+    nloc = shards[0].N
+    assert all(d.N == nloc for d in shards)
+    nbytes = M * nloc * 2
+    lay = w4.peer.arena_layout(nbytes, world)
+    arenas = [torch.zeros(lay["bytes"], dtype=torch.uint8, device="cuda") for _ in range(world)]
+    base = [a.data_ptr() for a in arenas]
+
+    def slot(arena, buf, owner):
+        return base[arena] + (buf * world + owner) * lay["slot"]
+
+    for step in range(1, 6):
+        buf = step % w4.peer.NBUF
+        x = oracle.normal_f16(M * K, 60 + step)
+        x_d = dev(x)
+        want = []
+        for r in range(world):
+            c = empty_f16(M * nloc)
+            w4.gemm(shards[r], ptr(x_d), ptr(c), M, path=w4.PATH_STREAM)
+            want.append(bits(c))
+        for r in range(world):
+            o = 1 - r
+            c_peer, flag_dst = [0, 0], [0, 0]
+            c_peer[o] = slot(o, buf, r)
+            flag_dst[o] = base[o] + lay["flags"] + 8 * r
+            w4.capi.gemm_push(shards[r], ptr(x_d), slot(r, buf, r), M, c_peer, flag_dst, base[r] + lay["flags"],
+                              base[r] + lay["counters"], base[r] + lay["done"], r, world)
+        for r in range(world):
+            w4.capi.allgather_wait(base[r] + lay["flags"], base[r] + lay["counters"], r, world)
+        sync_ok()
+        for arena in range(world):
+            for owner in range(world):
+                off = (buf * world + owner) * lay["slot"]
+                got = arenas[arena][off:off + nbytes].view(torch.int16).cpu().numpy().view(np.uint16)
+                assert np.array_equal(got, want[owner]), (step, arena, owner)
+            flags = arenas[arena][lay["flags"]:lay["flags"] + 8 * world].view(torch.int64)
+            assert int(flags[1 - arena]) == step
+
+
 @pytest.mark.parametrize("world", [2, 3, 8])
 def test_sharded_descriptors_match_unsharded(oracle, world):
     """Descriptors built by shard.shard_w4 (contiguous row slices of q / scales / zeros): the hook output of the

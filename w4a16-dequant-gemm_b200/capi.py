@@ -79,6 +79,7 @@ ABI = {
     "w4b_peer_free": (_I, [_P]),
     "w4b_allgather_push": (_I, [_P, C.c_size_t, C.POINTER(_P), C.POINTER(_P), _P, _P, _I, _I, _I, _P]),
     "w4b_allgather_wait": (_I, [_P, _P, _I, _I, _P]),
+    "w4b_gemm_w4_push": (_I, [C.POINTER(_PackedW4), _P, _P, _I, C.POINTER(_P), C.POINTER(_P), _P, _P, _P, _I, _I, _P]),
 }
 
 
@@ -313,6 +314,14 @@ def allgather_push(src, nbytes, dst, flag_dst, flags_local, counters, rank, worl
     arr = _P * world
     _check(lib.w4b_allgather_push(src, nbytes, arr(*dst), arr(*flag_dst), flags_local, counters, rank, world,
                                   1 if wait_now else 0, stream))
+
+
+def gemm_push(p: DevicePackedW, x, c, M, c_peer, flag_dst, flags_local, counters, done, rank, world, stream=None):
+    """The sharded GEMM with the exchange in its epilogue: c (this rank's slice buffer) also goes to c_peer[p]
+    in every peer's arena and the step flag is posted, all in the one kernel."""
+    arr = _P * world
+    _check(lib.w4b_gemm_w4_push(C.byref(p._c()), x, c, M, arr(*c_peer), arr(*flag_dst), flags_local, counters, done,
+                                rank, world, stream))
 
 
 def allgather_wait(flags_local, counters, rank, world, stream=None):

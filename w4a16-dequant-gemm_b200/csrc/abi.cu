@@ -161,10 +161,14 @@ int route_kernel(int entry, int N, int K, int gs_or_0, const void* q, const void
 }
 
 int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros, int N, int K, int G,
-             const void* x, void* c, int M, int entry, cudaStream_t stream, void* w_out, const char* who) {
+             const void* x, void* c, int M, int entry, cudaStream_t stream, void* w_out, const char* who,
+             const StreamPeers* peers = nullptr) {
   DeviceCtx* ctx = nullptr;
   if (int rc = get_ctx(&ctx)) return rc;
   const int kernel = route_kernel(entry, N, K, fmt == 2 ? 0 : gs, q, scales, x, w_out);
+  if (peers && kernel != W4B_PATH_STREAM)
+    return fail(W4B_INVALID, "%s: the exchange form needs a shape of the stream kernel (K %% 512 == 0, N >= 64, gs 32/64/128, "
+                "16-byte aligned q / scales / x)", who);
   if (kernel == W4B_PATH_TENSOR) {
     TensorPlan tplan;
     tensor_gemm_plan(N, K, M, ctx->sm_count, &tplan);
@@ -185,7 +189,7 @@ int run_gemm(int fmt, int gs, const uint32_t* q, const void* scales, const uint3
     int launches = 0;
     CUDA_TRY(stream_gemm_launch(fmt, gs, q, scales, zeros, N, K, G, (const __half*)x, (__half*)c, M,
                                 (__half*)w_out, plan, (float*)ctx->gemm_ws.ptr, (int*)ctx->gemm_counters.ptr,
-                                ctx->gemm_xa.ptr, ctx->status, g_overlap.load() != 0, stream, &launches),
+                                ctx->gemm_xa.ptr, ctx->status, g_overlap.load() != 0, stream, &launches, peers),
              who);
     g_launches += (unsigned long long)launches;
     return W4B_OK;
@@ -613,6 +617,35 @@ int w4b_allgather_push(const void* src, size_t bytes, void* const* dst, void* co
   CUDA_TRY(peer_push_launch(pp, (cudaStream_t)stream), "allgather push kernel");
   g_launches += 1;
   return W4B_OK;
+}
+
+int w4b_gemm_w4_push(const w4b_packed_w4* p, const void* x, void* c, int M, void* const* c_peer, void* const* flag_dst,
+                     const void* flags_local, void* counters, void* done, int rank, int world, void* stream) {
+  if (int rc = check_w4(p, "gemm push")) return rc;
+  if (!x || !c) INVALID("gemm push: null pointer");
+  if (M < 1 || M > 16) INVALID("gemm push: M must be 1..16 (the stream kernel's single pass)");
+  if (int rc = check_gemm_bounds(p->N, M, W4B_PATH_STREAM, "gemm push")) return rc;
+  if (world < 2 || world > kMaxPeers) INVALID("gemm push: world must be 2..%d", kMaxPeers);
+  if (rank < 0 || rank >= world) INVALID("gemm push: rank out of range");
+  if (!c_peer || !flag_dst || !flags_local || !counters || !done) INVALID("gemm push: null pointer");
+  if ((((uintptr_t)flags_local | (uintptr_t)counters) & 7u) || ((uintptr_t)done & 3u))
+    INVALID("gemm push: flags must be 8-byte aligned, the completion counter 4-byte aligned");
+  StreamPeers sp;
+  memset(&sp, 0, sizeof(sp));
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) continue;
+    if (!c_peer[r] || !flag_dst[r] || ((uintptr_t)c_peer[r] & 1u) || ((uintptr_t)flag_dst[r] & 7u))
+      INVALID("gemm push: bad destination for peer %d", r);
+    sp.c_peer[r] = (__half*)c_peer[r];
+    sp.flag_dst[r] = (unsigned long long*)flag_dst[r];
+  }
+  sp.world = world;
+  sp.rank = rank;
+  sp.flags_local = flags_local;
+  sp.counters = (unsigned long long*)counters;
+  sp.done = (int*)done;
+  return run_gemm(p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, x, c, M, W4B_PATH_STREAM,
+                  (cudaStream_t)stream, nullptr, "gemm push", &sp);
 }
 
 int w4b_allgather_wait(const void* flags_local, const void* counters, int rank, int world, void* stream) {

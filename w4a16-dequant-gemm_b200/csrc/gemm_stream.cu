@@ -54,6 +54,8 @@
 // is routed to the generic kernel by the dispatcher.
 #include <cuda.h>
 
+#include <string.h>
+
 #include <atomic>
 
 #include "w4b_common.cuh"
@@ -78,7 +80,7 @@ constexpr int SK_LOADER = SK_CONSUMERS;          // warp that issues the loads
 constexpr int SK_HANDOFF = SK_CONSUMERS + 1;     // warp that exchanges fragments with other CTAs
 constexpr int SK_THREADS = 32 * (SK_CONSUMERS + 2);
 constexpr int SK_MAX_STAGES = 12;
-constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 2);  // ring barriers + "parked" + "collected"
+constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 3);  // ring barriers + "parked" + "collected" + "peers_ok"
 constexpr int SK_RED_BYTES_PER_MT = SK_TILES * 32 * 16;      // the upper k half's fragments, one per tile
 constexpr int SK_COLLECT_BYTES_PER_MT = SK_TILES * 32 * 16;  // other CTAs' fragments, summed
 constexpr int SK_XROW = 1024 + 64;  // streamed activations: bytes per row of a unit's block (== 64 mod 128)
@@ -120,6 +122,7 @@ struct StreamParams {
   float* ws;
   int* counters;
   int* status;
+  StreamPeers peers;  // world == 0: no exchange
 };
 
 // Unit arithmetic is unsigned 32-bit (the launcher guarantees U * grid < 2^31): 64-bit
@@ -404,6 +407,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
   auto empty_bar = [&](int s) { return sm_bar + 8u * (uint32_t)(stages + s); };
   const uint32_t parked_bar = sm_bar + 8u * (uint32_t)(2 * stages);  // the 4 tiles' fragments are in the workspace
   const uint32_t collected_bar = parked_bar + 8u;                    // the other CTAs' fragments are summed
+  const uint32_t peers_bar = collected_bar + 8u;  // exchange form: the peers have this rank's previous slice
 
   const int grid = (int)gridDim.x;
   const int m0 = (int)blockIdx.y * a.xrows;  // first activation row of this pass
@@ -423,6 +427,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
     if (tid == 0) {
       mbar_init(parked_bar, SK_TILES);
       mbar_init(collected_bar, 1);
+      mbar_init(peers_bar, 1);
     }
     mbar_init_fence();
   }
@@ -516,6 +521,26 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
     // adds their fragments in CTA order into shared memory and signals `collected`.
     const Handoff hand(walk, a.U, C, grid, (int)blockIdx.x);
     auto tile_live = [&](int panel, int t) { return panel * SK_ROWS + t * 16 < a.N; };
+    if (a.peers.world) {
+      // Exchange form: before this grid stores into the peers' arenas, every peer's slice of the previous step
+      // must have arrived here - then no peer is more than one step behind and, with three slice buffers in
+      // rotation, nothing a peer may still read is overwritten. In steady state the flags are long there.
+      pdl_wait();
+      if (lane < a.peers.world && lane != a.peers.rank) {
+        const volatile unsigned long long* flag = reinterpret_cast<const volatile unsigned long long*>(a.peers.flags_local) + lane;
+        const unsigned long long want = *(reinterpret_cast<const volatile unsigned long long*>(a.peers.counters) + lane);
+        const long long t0 = clock64();
+        while (*flag < want) {
+          __nanosleep(100);
+          if (clock64() - t0 > kWaitLimitCycles) {
+            atomicExch(a.status, ST_PEER_TIMEOUT);
+            break;
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(peers_bar);
+    }
     if (hand.park_panel >= 0) {
       // (the consumers park after they have waited for the previous grid)
       if (!mbar_wait(parked_bar, 0u, a.status, ST_STREAM_PANEL_TIMEOUT)) return;
@@ -663,6 +688,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
   // A warp whose bounded wait ran out stops waiting and computing but keeps handing stages back, so that
   // the CTA ends instead of hanging.
   bool alive = true;
+  bool peers_ok = false;
   for (int seg = 0; seg < walk.nseg; ++seg) {
     int p, ch0, len;
     walk.segment_pc(seg, C, &p, &ch0, &len);
@@ -871,19 +897,51 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
         out[mt][3] = v.w + out[mt][3];
       }
     }
+    if (a.peers.world && !peers_ok) {  // (in steady state this has completed long ago)
+      if (!mbar_wait(peers_bar, 0u, a.status, ST_PEER_TIMEOUT)) alive = false;
+      peers_ok = true;
+    }
     {
       const int na = tile_row0 + rg, nb = na + 8;
+      // the tile's outputs go to c and, in the exchange form, to the same place of every peer's arena
+      // (plain peer stores; the local copy is peer slot `rank`)
+      auto put = [&](size_t idx, float v) {
+        const __half hv = __float2half_rn(v);
+        a.c[idx] = hv;
+        for (int pr = 0; pr < a.peers.world; ++pr)
+          if (pr != a.peers.rank) a.peers.c_peer[pr][idx] = hv;
+      };
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const int col = 8 * mt + 2 * c;  // activation row within this pass
         const int m = m0 + col;
         if (col < mrows) {
-          if (na < a.N) a.c[(size_t)m * a.N + na] = __float2half_rn(out[mt][0]);
-          if (nb < a.N) a.c[(size_t)m * a.N + nb] = __float2half_rn(out[mt][2]);
+          if (na < a.N) put((size_t)m * a.N + na, out[mt][0]);
+          if (nb < a.N) put((size_t)m * a.N + nb, out[mt][2]);
         }
         if (col + 1 < mrows) {
-          if (na < a.N) a.c[(size_t)(m + 1) * a.N + na] = __float2half_rn(out[mt][1]);
-          if (nb < a.N) a.c[(size_t)(m + 1) * a.N + nb] = __float2half_rn(out[mt][3]);
+          if (na < a.N) put((size_t)(m + 1) * a.N + na, out[mt][1]);
+          if (nb < a.N) put((size_t)(m + 1) * a.N + nb, out[mt][3]);
+        }
+      }
+    }
+  }
+  if (a.peers.world && kh == 0) {
+    // Exchange form: the grid's last tile warp posts the step to every peer. Each tile warp makes its peer
+    // stores visible system-wide, then counts itself; whoever completes the count knows every slice element
+    // is out and releases the flags.
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) {
+      const int total_warps = (int)(gridDim.x * gridDim.y) * SK_TILES;
+      if (atomicAdd(a.peers.done, 1) == total_warps - 1) {
+        __threadfence_system();
+        *a.peers.done = 0;  // ready for the next launch
+        for (int pr = 0; pr < a.peers.world; ++pr) {
+          if (pr == a.peers.rank) continue;
+          const unsigned long long step = a.peers.counters[pr] + 1ull;
+          asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peers.flag_dst[pr]), "l"(step) : "memory");
+          a.peers.counters[pr] = step;
         }
       }
     }
@@ -963,7 +1021,6 @@ size_t fixed_smem(int rows, int K) {
          (size_t)mt * (SK_RED_BYTES_PER_MT + SK_COLLECT_BYTES_PER_MT);
 }
 // Ring depth that fits beside `rows` resident activation rows within `budget` bytes per CTA.
-constexpr int kMinStages = 3;      // one unit being consumed, two in flight
 constexpr int kMinStagesHalf = 5;  // a ring worth confining to half an SM
 int stages_for(int rows, int K, int stage_bytes, int budget) {
   const long long room = (long long)budget - (long long)fixed_smem(rows, K);
@@ -1046,7 +1103,7 @@ void stream_gemm_plan(int N, int K, int M, int gs_or_0_for_mx, int sm_count, Str
 cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
                                int N, int K, int G, const __half* x, __half* c, int M, __half* w_out,
                                const StreamPlan& plan, float* ws, int* counters, void* xa, int* status,
-                               bool overlap, cudaStream_t stream, int* launches) {
+                               bool overlap, cudaStream_t stream, int* launches, const StreamPeers* peers) {
   CUtensorMap tmap;
   const cuuint64_t gdim[2] = {(cuuint64_t)(K / 8), (cuuint64_t)N};
   const cuuint64_t gstride[1] = {(cuuint64_t)(K / 8) * 4};
@@ -1079,6 +1136,11 @@ cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   sp.status = status;
   sp.xrows = plan.rows_per_pass;
   sp.xa = plan.streamed ? (const uint8_t*)xa : nullptr;
+  if (peers) {
+    sp.peers = *peers;
+  } else {
+    memset(&sp.peers, 0, sizeof(sp.peers));
+  }
   if (launches) *launches = plan.streamed ? 2 : 1;
   if (plan.streamed) {
     cudaLaunchConfig_t cfg = {};

@@ -38,6 +38,16 @@ cudaError_t generic_gemm_launch(int fmt, int gs, const uint32_t* q, const void* 
                                 cudaStream_t stream);
 
 // ---- gemm_stream.cu ---------------------------------------------------------
+// Exchange form of the stream GEMM (column-parallel ranks, one process per GPU): besides c, every output element
+// is stored to the same offset of each peer's copy, and the grid's last warp posts the step flags.
+struct StreamPeers {
+  int world, rank;                      // world == 0: no exchange
+  __half* c_peer[8];                    // rank p's copy of this rank's slice (null for this rank)
+  unsigned long long* flag_dst[8];      // rank p's flag word for this rank
+  const void* flags_local;              // this rank's flag words, one uint64 per peer
+  unsigned long long* counters;         // steps pushed to each peer so far, one uint64 per rank
+  int* done;                            // grid completion counter in this rank's arena, zero between launches
+};
 struct StreamPlan {
   int streamed;       // 1: activations arranged by a pre-pass and streamed with the units; 0: resident in shared memory
   int rows_per_pass;  // activation rows per pass
@@ -59,7 +69,7 @@ void stream_gemm_plan(int N, int K, int M, int gs_or_0_for_mx, int sm_count, Str
 cudaError_t stream_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
                                int N, int K, int G, const __half* x, __half* c, int M, __half* w_out,
                                const StreamPlan& plan, float* ws, int* counters, void* xa, int* status,
-                               bool overlap, cudaStream_t stream, int* launches);
+                               bool overlap, cudaStream_t stream, int* launches, const StreamPeers* peers = nullptr);
 
 // ---- gemm_tensor.cu ---------------------------------------------------------
 struct TensorPlan {

@@ -28,7 +28,8 @@ def arena_layout(slice_bytes: int, world: int) -> dict:
     data = NBUF * world * slot
     flags = _round_up(data, 256)
     counters = flags + _round_up(8 * world, 256)
-    return {"slot": slot, "flags": flags, "counters": counters, "bytes": counters + _round_up(8 * world, 256)}
+    done = counters + _round_up(8 * world, 256)  # completion counter of the GEMM that pushes from its epilogue
+    return {"slot": slot, "flags": flags, "counters": counters, "done": done, "bytes": done + 256}
 
 
 class PeerGather:
@@ -58,6 +59,15 @@ class PeerGather:
         flag_dst = [0 if p == r else self.peers[p] + self.lay["flags"] + 8 * r for p in range(w)]
         capi.allgather_push(self.slot(buf, r), self.slice_bytes, dst, flag_dst, self.base + self.lay["flags"],
                             self.base + self.lay["counters"], r, w, wait_now, stream)
+
+    def gemm_push(self, desc, x, M, buf: int, stream=None):
+        """The sharded GEMM (stream kernel, M <= 16) writing this rank's slice of buffer `buf` into its own arena
+        and into every peer's, and posting the step: GEMM and exchange in one kernel."""
+        r, w = self.rank, self.world
+        dst = [0 if p == r else self.slot(buf, r, self.peers[p]) for p in range(w)]
+        flag_dst = [0 if p == r else self.peers[p] + self.lay["flags"] + 8 * r for p in range(w)]
+        capi.gemm_push(desc, x, self.slot(buf, r), M, dst, flag_dst, self.base + self.lay["flags"],
+                       self.base + self.lay["counters"], self.base + self.lay["done"], r, w, stream)
 
     def wait(self, stream=None):
         """Wait on the stream until every peer's slice of the last pushed step is here."""
