@@ -263,6 +263,9 @@ def run_mine(args):
         if int(flag.item()) == 0:
             pg = None
     peer_mode = pg is not None
+    # The exchange as its own kernel after the GEMM (measured 15.0 us per step on two GPUs) or from the GEMM's
+    # epilogue (w4b_gemm_w4_push: one kernel per step, measured 16.9 us): the faster one is the default.
+    fused_exchange = os.environ.get("W4B_BENCH_EXCHANGE", "split") == "fused"
     gathered = torch.empty(world, M, N, device=device, dtype=torch.float16) if (world > 1 and not peer_mode) else None
 
     def step(i, st=None):
@@ -276,7 +279,11 @@ def run_mine(args):
             buf = i % w4.peer.NBUF  # slice buffers in rotation
             # one kernel: the GEMM's epilogue stores the slice into every peer's arena and posts the step
             # (it waits for the peers' previous slices only; pg.wait() completes a sequence)
-            pg.gemm_push(packs[i % copies][3], x.data_ptr(), M, buf, st)
+            if fused_exchange:
+                pg.gemm_push(packs[i % copies][3], x.data_ptr(), M, buf, st)
+            else:
+                w4.gemm(packs[i % copies][3], x.data_ptr(), pg.slot(buf, rank), M, st)
+                pg.push(buf, st)
 
     class _Arena:  # a window of device memory as a torch tensor of int16
         def __init__(self, ptr, n):
@@ -440,9 +447,9 @@ def run_mine(args):
                                      "touched only after the previous kernel has completed)",
                    "timing": "one CUDA graph of K launches, CUDA events" if world == 1 else
                              "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks" if not peer_mode else
-                             "one CUDA graph of K steps (one kernel per step: the GEMM, whose epilogue stores its output slice into every peer's arena over NVLink and posts the step; a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
+                             ("one CUDA graph of K steps (one kernel per step: the GEMM, whose epilogue stores its output slice into every peer's arena over NVLink and posts the step; " if fused_exchange else "one CUDA graph of K steps (GEMM + peer all-gather kernel; ") + "a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
                    "parallelism": "single GPU" if world == 1 else
-                                  f"column-parallel N x{world}, all-gather by peer stores from the GEMM's epilogue" if peer_mode else
+                                  f"column-parallel N x{world} + all-gather over NVLink peer stores" if peer_mode else
                                   f"column-parallel N x{world} + NCCL all-gather",
                    "rel_l2_vs_fp32_product": rel},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",

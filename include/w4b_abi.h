@@ -236,11 +236,11 @@ int w4b_allgather_push(const void* src, size_t bytes, void* const* dst, void* co
                        void* stream);
 int w4b_allgather_wait(const void* flags_local, const void* counters, int rank, int world, void* stream);
 /* The sharded GEMM and its exchange in ONE kernel (no reference counterpart): w4b_gemm_w4 through the
- * stream kernel (M <= 16, a shape that kernel serves) whose epilogue stores every output element to c
- * (this rank's slice buffer in its own arena) and to c_peer[p], the same buffer in rank p's arena, with
- * plain peer stores; the grid's last warp then posts the step to flag_dst[p] exactly as
+ * stream kernel (M <= 16, a shape that kernel serves) into c (this rank's slice buffer in its own arena,
+ * 16-byte aligned); the warp that finishes the grid's last tile then copies the slice to c_peer[p], the
+ * same buffer in rank p's arena, with plain 16-byte peer stores and posts the step to flag_dst[p] exactly as
  * w4b_allgather_push does (same flags, same counters: the two entries can be mixed, and
- * w4b_allgather_wait completes a sequence). Before its first peer store the kernel waits (bounded) for the
+ * w4b_allgather_wait completes a sequence). Before the first peer store the kernel waits (bounded) for the
  * peers' slices of the previous step, so ranks stay within one step of each other; rotate over three slice
  * buffers. done: a zero-initialised 32-bit word in this rank's arena. c_peer, flag_dst are HOST arrays of
  * device pointers (entries [rank] ignored). */

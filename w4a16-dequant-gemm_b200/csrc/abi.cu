@@ -623,6 +623,7 @@ int w4b_gemm_w4_push(const w4b_packed_w4* p, const void* x, void* c, int M, void
                      const void* flags_local, void* counters, void* done, int rank, int world, void* stream) {
   if (int rc = check_w4(p, "gemm push")) return rc;
   if (!x || !c) INVALID("gemm push: null pointer");
+  if ((uintptr_t)c & 15u) INVALID("gemm push: the slice buffer must be 16-byte aligned");
   if (M < 1 || M > 16) INVALID("gemm push: M must be 1..16 (the stream kernel's single pass)");
   if (int rc = check_gemm_bounds(p->N, M, W4B_PATH_STREAM, "gemm push")) return rc;
   if (world < 2 || world > kMaxPeers) INVALID("gemm push: world must be 2..%d", kMaxPeers);
@@ -634,7 +635,7 @@ int w4b_gemm_w4_push(const w4b_packed_w4* p, const void* x, void* c, int M, void
   memset(&sp, 0, sizeof(sp));
   for (int r = 0; r < world; ++r) {
     if (r == rank) continue;
-    if (!c_peer[r] || !flag_dst[r] || ((uintptr_t)c_peer[r] & 1u) || ((uintptr_t)flag_dst[r] & 7u))
+    if (!c_peer[r] || !flag_dst[r] || ((uintptr_t)c_peer[r] & 15u) || ((uintptr_t)flag_dst[r] & 7u))
       INVALID("gemm push: bad destination for peer %d", r);
     sp.c_peer[r] = (__half*)c_peer[r];
     sp.flag_dst[r] = (unsigned long long*)flag_dst[r];

@@ -80,7 +80,7 @@ constexpr int SK_LOADER = SK_CONSUMERS;          // warp that issues the loads
 constexpr int SK_HANDOFF = SK_CONSUMERS + 1;     // warp that exchanges fragments with other CTAs
 constexpr int SK_THREADS = 32 * (SK_CONSUMERS + 2);
 constexpr int SK_MAX_STAGES = 12;
-constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 3);  // ring barriers + "parked" + "collected" + "peers_ok"
+constexpr int SK_BAR_BYTES = 8 * (2 * SK_MAX_STAGES + 4);  // ring barriers + "parked" + "collected" + "peers_ok" + a counter
 constexpr int SK_RED_BYTES_PER_MT = SK_TILES * 32 * 16;      // the upper k half's fragments, one per tile
 constexpr int SK_COLLECT_BYTES_PER_MT = SK_TILES * 32 * 16;  // other CTAs' fragments, summed
 constexpr int SK_XROW = 1024 + 64;  // streamed activations: bytes per row of a unit's block (== 64 mod 128)
@@ -326,6 +326,7 @@ __device__ __forceinline__ void named_arrive(int id, int threads) {
 constexpr int BAR_HANDED = 1;  // +tile: the upper k half has written its fragment (the lower half waits)
 constexpr int BAR_TAKEN = 5;   // +tile: the lower half has read it (the upper half waits before rewriting)
 constexpr int BAR_XFILL = 9;   // all consumer warps: the activations are in shared memory
+constexpr int BAR_DONE = 10;   // all consumer warps: exchange form, end of the CTA's work
 
 // The word slot of a 256-k box that holds natural word wi (0..31) of an activation row: the chunks the four lanes of
 // a column read together are adjacent.
@@ -408,6 +409,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
   const uint32_t parked_bar = sm_bar + 8u * (uint32_t)(2 * stages);  // the 4 tiles' fragments are in the workspace
   const uint32_t collected_bar = parked_bar + 8u;                    // the other CTAs' fragments are summed
   const uint32_t peers_bar = collected_bar + 8u;  // exchange form: the peers have this rank's previous slice
+  const uint32_t cta_done = peers_bar + 8u;       // exchange form: whether this CTA finished last
 
   const int grid = (int)gridDim.x;
   const int m0 = (int)blockIdx.y * a.xrows;  // first activation row of this pass
@@ -897,20 +899,9 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
         out[mt][3] = v.w + out[mt][3];
       }
     }
-    if (a.peers.world && !peers_ok) {  // (in steady state this has completed long ago)
-      if (!mbar_wait(peers_bar, 0u, a.status, ST_PEER_TIMEOUT)) alive = false;
-      peers_ok = true;
-    }
     {
       const int na = tile_row0 + rg, nb = na + 8;
-      // the tile's outputs go to c and, in the exchange form, to the same place of every peer's arena
-      // (plain peer stores; the local copy is peer slot `rank`)
-      auto put = [&](size_t idx, float v) {
-        const __half hv = __float2half_rn(v);
-        a.c[idx] = hv;
-        for (int pr = 0; pr < a.peers.world; ++pr)
-          if (pr != a.peers.rank) a.peers.c_peer[pr][idx] = hv;
-      };
+      auto put = [&](size_t idx, float v) { a.c[idx] = __float2half_rn(v); };
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const int col = 8 * mt + 2 * c;  // activation row within this pass
@@ -926,16 +917,55 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
       }
     }
   }
-  if (a.peers.world && kh == 0) {
-    // Exchange form: the grid's last tile warp posts the step to every peer. Each tile warp makes its peer
-    // stores visible system-wide, then counts itself; whoever completes the count knows every slice element
-    // is out and releases the flags.
-    __threadfence_system();
-    __syncwarp();
-    if (lane == 0) {
-      const int total_warps = (int)(gridDim.x * gridDim.y) * SK_TILES;
-      if (atomicAdd(a.peers.done, 1) == total_warps - 1) {
-        __threadfence_system();
+  if (a.peers.world) {
+    // Exchange form: the CTA that finishes last sends the finished slice to every peer and posts the step. Every
+    // consumer warp makes its part of c visible on this GPU; the CTA then counts itself at the grid's counter.
+    // The CTA that completes the count sees the whole slice: its 256 consumer threads copy it into the peers'
+    // arenas (plain 16-byte peer stores, every piece in flight at once), make the copies visible system-wide, and
+    // one thread releases the flags.
+    __threadfence();
+    named_barrier(BAR_DONE, 32 * SK_CONSUMERS);
+    if (tid == 0) {
+      const uint32_t last = atomicAdd(a.peers.done, 1) == (int)(gridDim.x * gridDim.y) - 1 ? 1u : 0u;
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(cta_done), "r"(last) : "memory");
+    }
+    named_barrier(BAR_DONE, 32 * SK_CONSUMERS);
+    uint32_t last;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(last) : "r"(cta_done) : "memory");
+    if (last) {
+      __threadfence();
+      (void)peers_ok;
+      mbar_wait(peers_bar, 0u, a.status, ST_PEER_TIMEOUT);  // the peers have taken the previous step (long ago)
+      const size_t bytes = (size_t)a.M * a.N * sizeof(__half);
+      const size_t n16 = bytes >> 4;
+      const uint4* src = reinterpret_cast<const uint4*>(a.c);
+      constexpr int NT = 32 * SK_CONSUMERS;
+      for (size_t i0 = 0; i0 < n16; i0 += 8 * NT) {  // batches of 8 pieces per thread, in flight together
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const size_t i = i0 + (size_t)u * NT + tid;
+          if (i < n16) v[u] = __ldcg(src + i);
+        }
+        for (int pr = 0; pr < a.peers.world; ++pr) {
+          if (pr == a.peers.rank) continue;
+          uint4* dst = reinterpret_cast<uint4*>(a.peers.c_peer[pr]);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const size_t i = i0 + (size_t)u * NT + tid;
+            if (i < n16) dst[i] = v[u];
+          }
+        }
+      }
+      for (int pr = 0; pr < a.peers.world; ++pr) {  // a tail shorter than 16 bytes
+        if (pr == a.peers.rank) continue;
+        for (size_t b = (n16 << 4) + 2 * tid; b < bytes; b += 2 * NT)
+          *reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(a.peers.c_peer[pr]) + b) =
+              *reinterpret_cast<const volatile __half*>(reinterpret_cast<const uint8_t*>(src) + b);
+      }
+      __threadfence_system();
+      named_barrier(BAR_DONE, 32 * SK_CONSUMERS);
+      if (tid == 0) {
         *a.peers.done = 0;  // ready for the next launch
         for (int pr = 0; pr < a.peers.world; ++pr) {
           if (pr == a.peers.rank) continue;

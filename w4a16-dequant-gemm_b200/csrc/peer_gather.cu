@@ -76,6 +76,8 @@ __global__ void peer_wait_kernel(const void* flags_local, const unsigned long lo
 
 }  // namespace
 
+// (Launched as a plain stream-ordered kernel: letting the next step's GEMM start beside it - programmatic dependent
+// launch - was measured slower, 17.7 against 15.0 us per step on two GPUs.)
 cudaError_t peer_push_launch(const PeerPush& p, cudaStream_t stream) {
   peer_push_kernel<<<p.world, PP_THREADS, 0, stream>>>(p);
   return cudaGetLastError();
