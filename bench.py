@@ -428,6 +428,9 @@ def run_mine(args):
     extra = {}
     if rank == 0 and world == 1 and not args.no_sweep:
         extra = sweep(torch, w4, device, packs, copies)
+    if not args.no_sweep:
+        del packs  # (room for the sharded problems)
+        extra["sharded"] = sharded_steps(torch, w4, device, world, rank, dist)
 
     cpu = cpu_baseline(quick=True) if (rank == 0 and world == 1) else None
     if world > 1:
@@ -652,6 +655,107 @@ def sweep(torch, w4, device, packs, copies):
     flash_case(256, 8192, 128, 32, "C4_BH256_S8192", paged=True)
     flash_case(512, 32768, 128, 32, "C4_BH512_S32768")
     flash_case(8, 1024, 128, 32, "C4_BH8_S1024_launch_bound")
+    assert w4.device_status() == 0
+    return out
+
+
+def sharded_steps(torch, w4, device, world, rank, dist):
+    """The metric the way the multi-GPU split is stated: ONE problem sharded over the ranks (strong scaling) - GEMMs
+    column-parallel along N (shard.shard_w4 slices of one matrix), decode attention across heads - with per-GPU
+    microseconds (max over ranks). Config 2's headline GEMM at M = 1, and config 5: the four linears of the
+    70B-shaped step at M = 16 (W4 symmetric gs = 128) and its paged W4 KV attention (64 sequences of 4608
+    positions = 256 shared prefix pages + 32 own pages of 16 tokens, 64 heads, D = 128, gs = 32), through the
+    batched paged entry. Gathers of the outputs are not in these numbers (the headline line times GEMM + exchange)."""
+    peak, _ = measured_peak()
+    out = {"n_gpus": world}
+
+    def tmax(us):
+        if world == 1:
+            return us
+        t = torch.tensor([us], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def time_sharded_gemm(Nf, K, gs, M, asym):
+        n0, n1 = w4.shard.row_range(Nf, world, rank)
+        nl = max(n1 - n0, 64)  # (a rank without rows still runs a minimal shard so that every rank times something)
+        nb = alg_bytes(nl, K, gs, M, asym=asym)
+        ncp = max(2, -(-300_000_000 // nb))
+        packs = []
+        for i in range(ncp):
+            qp = torch.randint(-2**31, 2**31 - 1, (nl, K // 8), device=device, dtype=torch.int32)
+            sc = (torch.rand(nl, K // gs, device=device) * 0.004 + 0.002).to(torch.float16)
+            zp = torch.randint(-2**31, 2**31 - 1, (nl, (K // gs + 7) // 8), device=device, dtype=torch.int32) if asym else None
+            packs.append((qp, sc, zp, w4.DevicePackedW(nl, K, gs, K // gs, 0 if asym else 1, qp.data_ptr(), sc.data_ptr(),
+                                                       zp.data_ptr() if asym else None)))
+        x = torch.randn(M, K, device=device).to(torch.float16)
+        c = torch.empty(M, nl, device=device, dtype=torch.float16)
+        for i in range(3):
+            w4.gemm(packs[i % ncp][3], x.data_ptr(), c.data_ptr(), M)
+        us = tmax(time_graph(torch, lambda i, s: w4.gemm(packs[i % ncp][3], x.data_ptr(), c.data_ptr(), M, s), max(4 * ncp, 24)))
+        del packs
+        return us, nb
+
+    us, nb = time_sharded_gemm(N_ROWS, K_COLS, GS, 1, True)
+    full = alg_bytes(N_ROWS, K_COLS, GS, 1)
+    out["C2_headline_sharded"] = {"us_per_gpu": round(us, 2), "rows_per_gpu": w4.shard.row_range(N_ROWS, world, 0)[1],
+                                  "aggregate_GBps": round(full / us / 1e3, 1),
+                                  "per_gpu_frac_of_measured_hbm": round(nb / us / 1e3 / peak, 3)}
+    lin = {}
+    tot_us = tot_roof = 0.0
+    for (Nf, K5) in ((10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672)):
+        us, nb = time_sharded_gemm(Nf, K5, GS, 16, False)
+        lin[f"N{Nf}_K{K5}"] = {"us_per_gpu": round(us, 2), "roof_us": round(nb / peak / 1e3, 2)}
+        tot_us += us
+        tot_roof += nb / peak / 1e3
+    lin["four_linears"] = {"us_per_gpu": round(tot_us, 2), "roof_us": round(tot_roof, 2), "frac_of_roof": round(tot_roof / tot_us, 3)}
+    out["C5_linears_M16"] = lin
+
+    # config 5 attention: this rank's heads of the 64
+    H, D, g, page, nseq, SP, SU = 64, 128, 32, 16, 64, 4096, 512
+    h0, h1 = w4.shard.head_range(H, world, rank)
+    hl = max(h1 - h0, 1)
+    G, S = D // g, SP + SU
+    npre, nown = SP // page, SU // page
+    npages = npre + nseq * nown  # 2304
+    rows = npages * page
+    gen = torch.Generator(device=device).manual_seed(11)
+    perm = torch.randperm(npages, generator=gen, device=device).to(torch.int32)
+    bt = torch.stack([torch.cat([perm[:npre], perm[npre + i * nown: npre + (i + 1) * nown]]) for i in range(nseq)]).contiguous()
+    lens = torch.full((nseq,), S, device=device, dtype=torch.int32)
+    unique = 2 * hl * rows * (D // 2 + G * 2)
+    npool = max(2, -(-200_000_000 // unique))  # rotate over pools ("layers") so that the step reads HBM, not L2
+    pools = []
+    for i in range(npool):
+        qk = torch.randint(-2**31, 2**31 - 1, (hl, rows, D // 8), device=device, dtype=torch.int32)
+        qv = torch.randint(-2**31, 2**31 - 1, (hl, rows, D // 8), device=device, dtype=torch.int32)
+        sk = (torch.rand(hl, rows, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        sv = (torch.rand(hl, rows, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        pools.append((qk, qv, sk, sv, w4.DeviceKVW4(hl, S, D, g, G, 1, qk.data_ptr(), sk.data_ptr(), None, qv.data_ptr(),
+                                                    sv.data_ptr(), None)))
+    q = torch.randn(nseq, hl, D, device=device, dtype=torch.float16)
+    o = torch.empty(nseq, hl, D, device=device, dtype=torch.float16)
+    call = lambda i, s=None: w4.attention_w4_flash_paged_batched(pools[i % npool][4], bt.data_ptr(), bt.shape[1], lens.data_ptr(),
+                                                                nseq, S, page, npages, q.data_ptr(), o.data_ptr(), s)
+    for i in range(2):
+        call(i)
+    us = tmax(time_graph(torch, call, max(2 * npool, 6)))
+    logical = 2 * nseq * hl * S * (D // 2 + G * 2)
+    out["C5_paged_attention"] = {"us_per_gpu": round(us, 1), "heads_per_gpu": hl, "unique_bytes": unique,
+                                 "GBps_on_unique_bytes": round(unique / us / 1e3, 1),
+                                 "frac_of_measured_hbm_on_unique_bytes": round(unique / us / 1e3 / peak, 3),
+                                 "logical_bytes": logical, "GBps_on_logical_bytes": round(logical / us / 1e3, 1),
+                                 "roof_us_unique": round(unique / peak / 1e3, 2)}
+    # 64 single-sequence calls of the reference-shaped entry, for comparison (one sequence per call)
+    d1 = pools[0][4]
+    def per_seq(i, s=None):
+        for sq in range(nseq):
+            w4.attention_w4_flash_paged(d1, bt.data_ptr() + 4 * sq * bt.shape[1], page, npages, q.data_ptr() + 2 * sq * hl * D,
+                                        o.data_ptr() + 2 * sq * hl * D, s)
+    per_seq(0)
+    us1 = tmax(time_graph(torch, per_seq, 3))
+    out["C5_paged_attention"]["us_per_gpu_64_single_sequence_calls"] = round(us1, 1)
+    out["C5_step_per_gpu_us"] = round(tot_us + us, 1)
     assert w4.device_status() == 0
     return out
 
