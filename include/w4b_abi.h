@@ -163,6 +163,38 @@ int w4b_dequant_mx(const w4b_packed_mx* p, void* w, void* stream);
 /* dequant_f8 (include/w4/kvflash.cuh:435-457): one head, q S*D bytes, s S*G. */
 int w4b_dequant_f8(const uint8_t* q, const uint16_t* s, void* w, int S, int D, int gs, void* stream);
 
+/* ---- device-side quantizers and KV append -------------------------------- */
+
+/* The reference quantises on the host only; a decode loop has to quantise the new
+ * token's K / V on the device. These entries run the host quantizers' arithmetic
+ * (FP64, operation for operation) in CUDA kernels and produce the same bits from the
+ * same values. Sources are device arrays of FP64 (`*_is_f16` == 0: what the host
+ * quantizers take) or FP16 values (converted exactly). What the host quantizers throw
+ * on for VALUES (NaN / infinity, a scale that overflows FP16 or underflows to zero on a
+ * non-zero group, an MX exponent above 127) cannot throw here: the kernel records
+ * status 501 in the device status word (w4b_device_status) and zeroes the group.
+ *
+ * w4b_quantize_w4: quantize (include/w4/pack.hpp:64-130); q N*words(K), scales N*G,
+ *   zeros N*words(G) (asymmetric only, else NULL).
+ * w4b_quantize_mx: quantize_mx (include/w4/mx.hpp:71-119); scales N*ceil(K/32) bytes.
+ * w4b_quantize_f8: one side of quantize_cache_f8 (include/w4/kvfp8.hpp:70-128):
+ *   rows*D bytes and rows*G FP16 scales.
+ * w4b_kv_append_w4: quantises one token - k_new / v_new hold H*D values - into row
+ *   `row` of every head slab of the cache p (slab_rows rows per head: S for a
+ *   contiguous cache, npages*page for a paged pool, where the caller resolves
+ *   row = bt[t/page]*page + t%page); the same bits quantize_cache
+ *   (include/w4/kvcache.hpp:60-108) gives that position. p->S is ignored.
+ * w4b_kv_append_f8: the same for an FP8 cache (contiguous: S rows per head). */
+int w4b_quantize_w4(const void* w, int w_is_f16, int N, int K, int gs, int symmetric, uint32_t* q,
+                    uint16_t* scales, uint32_t* zeros, void* stream);
+int w4b_quantize_mx(const void* w, int w_is_f16, int N, int K, uint32_t* q, uint8_t* scales, void* stream);
+int w4b_quantize_f8(const void* x, int x_is_f16, int rows, int D, int gs, uint8_t* q, uint16_t* scales,
+                    void* stream);
+int w4b_kv_append_w4(const w4b_kv_w4* p, long long row, long long slab_rows, const void* k_new,
+                     const void* v_new, int new_is_f16, void* stream);
+int w4b_kv_append_f8(const w4b_kv_f8* p, long long row, const void* k_new, const void* v_new,
+                     int new_is_f16, void* stream);
+
 /* ---- decode attention, one query token per head ----------------------- */
 
 /* attention_fp16_flash (include/w4/kvflash.cuh:365-384): q H*D, k16/v16

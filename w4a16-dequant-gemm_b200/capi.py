@@ -66,6 +66,11 @@ ABI = {
     "w4b_dequant_w4": (_I, [C.POINTER(_PackedW4), _P, _P]),
     "w4b_dequant_mx": (_I, [C.POINTER(_PackedMx), _P, _P]),
     "w4b_dequant_f8": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "w4b_quantize_w4": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "w4b_quantize_mx": (_I, [_P, _I, _I, _I, _P, _P, _P]),
+    "w4b_quantize_f8": (_I, [_P, _I, _I, _I, _I, _P, _P, _P]),
+    "w4b_kv_append_w4": (_I, [C.POINTER(_KvW4), C.c_longlong, C.c_longlong, _P, _P, _I, _P]),
+    "w4b_kv_append_f8": (_I, [C.POINTER(_KvF8), C.c_longlong, _P, _P, _I, _P]),
     "w4b_attn_flash_fp16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "w4b_attn_flash_w4": (_I, [C.POINTER(_KvW4), _P, _P, _P, _P, _P]),
     "w4b_attn_flash_f8": (_I, [C.POINTER(_KvF8), _P, _P, _P, _P, _P]),
@@ -262,6 +267,29 @@ def attention_fp16(q, k16, v16, out, H, S, D, stream=None):  # kvattention.cuh:2
 
 def attention_w4(p: DeviceKVW4, q, out, stream=None, k_out=None, v_out=None):  # kvattention.cuh:241
     _check(lib.w4b_attn_single_w4(C.byref(p._c()), q, out, stream, k_out, v_out))
+
+
+# ---- device-side quantizers and KV append (the reference quantises on the host only) ------------
+
+def quantize(w, N, K, gs, symmetric, q, scales, zeros=None, f16=False, stream=None):  # pack.hpp:64
+    _check(lib.w4b_quantize_w4(w, int(f16), N, K, gs, int(symmetric), q, scales, zeros, stream))
+
+
+def quantize_mx(w, N, K, q, scales, f16=False, stream=None):  # mx.hpp:71
+    _check(lib.w4b_quantize_mx(w, int(f16), N, K, q, scales, stream))
+
+
+def quantize_f8(x, rows, D, gs, q, scales, f16=False, stream=None):  # kvfp8.hpp:70 (one side)
+    _check(lib.w4b_quantize_f8(x, int(f16), rows, D, gs, q, scales, stream))
+
+
+def kv_append_w4(p: DeviceKVW4, row, slab_rows, k_new, v_new, f16=False, stream=None):
+    """Quantise one token's K / V (H*D values each) into row `row` of every head slab of a W4 cache."""
+    _check(lib.w4b_kv_append_w4(C.byref(p._c()), row, slab_rows, k_new, v_new, int(f16), stream))
+
+
+def kv_append_f8(p: DeviceKVF8, row, k_new, v_new, f16=False, stream=None):
+    _check(lib.w4b_kv_append_f8(C.byref(p._c()), row, k_new, v_new, int(f16), stream))
 
 
 def device_status() -> int:

@@ -365,6 +365,90 @@ int w4b_dequant_f8(const uint8_t* q, const uint16_t* s, void* w, int S, int D, i
   return W4B_OK;
 }
 
+// ---- device-side quantizers and KV append (no device counterpart in the reference) ------------
+
+int w4b_quantize_w4(const void* w, int w_is_f16, int N, int K, int gs, int symmetric, uint32_t* q, uint16_t* scales,
+                    uint32_t* zeros, void* stream) {
+  // the host quantizer's shape contract (pack.hpp:66-75)
+  if (N < 1 || K < 1) INVALID("quantize: bad dims");
+  if (gs < 8 || gs % 8 != 0) INVALID("quantize: gs must be a multiple of 8");
+  if (!w || !q || !scales) INVALID("quantize: null pointer");
+  if (!symmetric && !zeros) INVALID("quantize: asymmetric without zeros");
+  if (symmetric && zeros) INVALID("quantize: symmetric carries no zeros");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(quantize_w4_launch(w, w_is_f16, N, K, gs, symmetric ? 1 : 0, 1, 0, q, (__half*)scales, zeros, ctx->status,
+                              (cudaStream_t)stream),
+           "quantize kernel");
+  g_launches += 1;
+  return W4B_OK;
+}
+
+int w4b_quantize_mx(const void* w, int w_is_f16, int N, int K, uint32_t* q, uint8_t* scales, void* stream) {
+  if (N < 1 || K < 1) INVALID("quantize_mx: bad dims");  // mx.hpp:73-77
+  if (!w || !q || !scales) INVALID("quantize_mx: null pointer");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(quantize_mx_launch(w, w_is_f16, N, K, q, scales, ctx->status, (cudaStream_t)stream), "quantize_mx kernel");
+  g_launches += 1;
+  return W4B_OK;
+}
+
+int w4b_quantize_f8(const void* x, int x_is_f16, int rows, int D, int gs, uint8_t* q, uint16_t* scales, void* stream) {
+  if (rows < 1 || D < 1) INVALID("quantize_f8: bad dims");  // kvfp8.hpp:72-80
+  if (gs < 8 || gs % 8 != 0) INVALID("quantize_f8: gs must be a multiple of 8");
+  if (!x || !q || !scales) INVALID("quantize_f8: null pointer");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(quantize_f8_launch(x, x_is_f16, rows, D, gs, 1, 0, q, (__half*)scales, ctx->status, (cudaStream_t)stream),
+           "quantize_f8 kernel");
+  g_launches += 1;
+  return W4B_OK;
+}
+
+int w4b_kv_append_w4(const w4b_kv_w4* p, long long row, long long slab_rows, const void* k_new, const void* v_new,
+                     int new_is_f16, void* stream) {
+  if (!p) INVALID("kv append: null descriptor");
+  if (p->H < 1 || p->D < 1) INVALID("kv append: bad dims");
+  if (p->gs < 8 || p->gs % 8 != 0) INVALID("kv append: gs must be a multiple of 8");
+  if (p->G != (p->D + p->gs - 1) / p->gs) INVALID("kv append: G inconsistent with D, gs");
+  if (!p->q_k || !p->s_k || !p->q_v || !p->s_v || !k_new || !v_new) INVALID("kv append: null pointer");
+  if (!p->symmetric && (!p->z_k || !p->z_v)) INVALID("kv append: asymmetric without zeros");
+  if (p->symmetric && (p->z_k || p->z_v)) INVALID("kv append: symmetric carries zeros");
+  if (slab_rows < 1 || row < 0 || row >= slab_rows) INVALID("kv append: row outside the head slab");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  const int sym = p->symmetric ? 1 : 0;
+  CUDA_TRY(quantize_w4_launch(k_new, new_is_f16, p->H, p->D, p->gs, sym, slab_rows, row, (uint32_t*)p->q_k, (__half*)p->s_k,
+                              (uint32_t*)p->z_k, ctx->status, (cudaStream_t)stream),
+           "kv append kernel");
+  CUDA_TRY(quantize_w4_launch(v_new, new_is_f16, p->H, p->D, p->gs, sym, slab_rows, row, (uint32_t*)p->q_v, (__half*)p->s_v,
+                              (uint32_t*)p->z_v, ctx->status, (cudaStream_t)stream),
+           "kv append kernel");
+  g_launches += 2;
+  return W4B_OK;
+}
+
+int w4b_kv_append_f8(const w4b_kv_f8* p, long long row, const void* k_new, const void* v_new, int new_is_f16,
+                     void* stream) {
+  if (!p) INVALID("kv f8 append: null descriptor");
+  if (p->H < 1 || p->S < 1 || p->D < 1) INVALID("kv f8 append: bad dims");
+  if (p->gs < 8 || p->gs % 8 != 0) INVALID("kv f8 append: gs must be a multiple of 8");
+  if (p->G != (p->D + p->gs - 1) / p->gs) INVALID("kv f8 append: G inconsistent with D, gs");
+  if (!p->q_k || !p->s_k || !p->q_v || !p->s_v || !k_new || !v_new) INVALID("kv f8 append: null pointer");
+  if (row < 0 || row >= p->S) INVALID("kv f8 append: row outside the head slab");
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(quantize_f8_launch(k_new, new_is_f16, p->H, p->D, p->gs, p->S, row, (uint8_t*)p->q_k, (__half*)p->s_k, ctx->status,
+                              (cudaStream_t)stream),
+           "kv f8 append kernel");
+  CUDA_TRY(quantize_f8_launch(v_new, new_is_f16, p->H, p->D, p->gs, p->S, row, (uint8_t*)p->q_v, (__half*)p->s_v, ctx->status,
+                              (cudaStream_t)stream),
+           "kv f8 append kernel");
+  g_launches += 2;
+  return W4B_OK;
+}
+
 // ---- decode attention ------------------------------------------------------
 
 namespace {

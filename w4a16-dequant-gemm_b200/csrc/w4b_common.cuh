@@ -25,6 +25,7 @@ enum : int {
   ST_TENSOR_TIMEOUT = 201,        // tensor GEMM: a pipeline wait ran out
   ST_FLASH_TIMEOUT = 301,         // flash decode: a pipeline wait ran out
   ST_PEER_TIMEOUT = 401,          // peer all-gather: a peer's slice never arrived
+  ST_QUANT_INVALID = 501,         // device quantizer: a value or scale the host quantizer would have thrown on
 };
 
 // --------------------------------------------------------------------------

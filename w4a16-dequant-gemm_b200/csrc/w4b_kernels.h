@@ -31,6 +31,16 @@ cudaError_t dequant_mx_launch(const uint32_t* q, const uint8_t* scales, int N, i
 cudaError_t dequant_f8_launch(const uint8_t* q, const __half* s, __half* w, int S, int D, int gs,
                               cudaStream_t stream);
 
+// ---- quantize.cu ---------------------------------------------------------------
+// f16: the source holds FP16 values, else FP64. Destination row of source row n: n * out_mul + out_add.
+cudaError_t quantize_w4_launch(const void* w, int f16, int N, int K, int gs, int symmetric, long long out_mul,
+                               long long out_add, uint32_t* q, __half* scales, uint32_t* zeros, int* status,
+                               cudaStream_t stream);
+cudaError_t quantize_mx_launch(const void* w, int f16, int N, int K, uint32_t* q, uint8_t* scales, int* status,
+                               cudaStream_t stream);
+cudaError_t quantize_f8_launch(const void* x, int f16, int rows, int D, int gs, long long out_mul, long long out_add,
+                               uint8_t* q, __half* scales, int* status, cudaStream_t stream);
+
 // ---- gemm_generic.cu --------------------------------------------------------
 // fmt: 0 = W4 symmetric, 1 = W4 asymmetric, 2 = MXFP4 (gs ignored, G = blocks per row).
 cudaError_t generic_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
