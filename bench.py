@@ -756,6 +756,58 @@ def sharded_steps(torch, w4, device, world, rank, dist):
     us1 = tmax(time_graph(torch, per_seq, 3))
     out["C5_paged_attention"]["us_per_gpu_64_single_sequence_calls"] = round(us1, 1)
     out["C5_step_per_gpu_us"] = round(tot_us + us, 1)
+    del pools
+
+    # The decode step as ONE graph per layer: qkv linear -> device-side append of the new token's K / V into the paged
+    # pool -> batched paged attention -> output, gate/up and down linears; launch overlap on between the stream GEMMs.
+    # Layers rotate so that the weights and pools come from HBM. Inputs of each linear are resident buffers of the
+    # right shape (the gathers between the linears are the exchange the headline line times; they are not in here).
+    shapes = ((10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672))
+    per_layer = sum(alg_bytes(max(w4.shard.row_range(Nf, world, rank)[1] - w4.shard.row_range(Nf, world, rank)[0], 64), K5, GS, 16,
+                              asym=False) for Nf, K5 in shapes) + unique
+    nlayers = max(2, -(-300_000_000 // per_layer))
+    layers = []
+    for li in range(nlayers):
+        lin_d = []
+        for (Nf, K5) in shapes:
+            n0, n1 = w4.shard.row_range(Nf, world, rank)
+            nl = max(n1 - n0, 64)
+            qp = torch.randint(-2**31, 2**31 - 1, (nl, K5 // 8), device=device, dtype=torch.int32)
+            sc = (torch.rand(nl, K5 // GS, device=device) * 0.004 + 0.002).to(torch.float16)
+            lin_d.append((qp, sc, w4.DevicePackedW(nl, K5, GS, K5 // GS, 1, qp.data_ptr(), sc.data_ptr(), None),
+                          torch.empty(16, nl, device=device, dtype=torch.float16)))
+        qk = torch.randint(-2**31, 2**31 - 1, (hl, rows, D // 8), device=device, dtype=torch.int32)
+        qv = torch.randint(-2**31, 2**31 - 1, (hl, rows, D // 8), device=device, dtype=torch.int32)
+        sk = (torch.rand(hl, rows, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        sv = (torch.rand(hl, rows, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        kvd = w4.DeviceKVW4(hl, S, D, g, G, 1, qk.data_ptr(), sk.data_ptr(), None, qv.data_ptr(), sv.data_ptr(), None)
+        layers.append((lin_d, (qk, qv, sk, sv), kvd))
+    x8 = torch.randn(16, 8192, device=device).to(torch.float16)
+    x28 = torch.randn(16, 28672, device=device).to(torch.float16)
+    knew = torch.randn(hl, D, device=device).to(torch.float16)
+    vnew = torch.randn(hl, D, device=device).to(torch.float16)
+    last_row = int(bt[0, -1].item()) * page + page - 1  # the newest position of sequence 0
+
+    def decode_step(i, s=None):
+        lin_d, _, kvd = layers[i % nlayers]
+        w4.gemm(lin_d[0][2], x8.data_ptr(), lin_d[0][3].data_ptr(), 16, s)
+        w4.kv_append_w4(kvd, last_row, rows, knew.data_ptr(), vnew.data_ptr(), True, s)
+        w4.attention_w4_flash_paged_batched(kvd, bt.data_ptr(), bt.shape[1], lens.data_ptr(), nseq, S, page, npages,
+                                            q.data_ptr(), o.data_ptr(), s)
+        w4.gemm(lin_d[1][2], x8.data_ptr(), lin_d[1][3].data_ptr(), 16, s)
+        w4.gemm(lin_d[2][2], x8.data_ptr(), lin_d[2][3].data_ptr(), 16, s)
+        w4.gemm(lin_d[3][2], x28.data_ptr(), lin_d[3][3].data_ptr(), 16, s)
+
+    for i in range(nlayers):
+        decode_step(i)
+    n0 = w4.launch_count()
+    decode_step(0)
+    per_step = w4.launch_count() - n0
+    us_step = tmax(time_graph(torch, decode_step, max(2 * nlayers, 4)))
+    out["C5_decode_step_graph"] = {"us_per_gpu_per_layer": round(us_step, 1), "kernel_launches_per_layer": int(per_step),
+                                   "sum_of_separately_timed_parts_us": round(tot_us + us, 1), "layers_rotated": nlayers,
+                                   "chain": "qkv linear, K/V append (device quantizer), batched paged attention, "
+                                            "o / gate-up / down linears; one CUDA graph, launch overlap on"}
     assert w4.device_status() == 0
     return out
 

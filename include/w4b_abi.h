@@ -219,9 +219,15 @@ int w4b_attn_flash_w4_paged(const w4b_kv_w4* p, const int* bt, int page, int npa
  * positions (device array, 1 <= seq_lens[i] <= max_seq_len; max_seq_len is a host
  * value that sizes the launch) and the block table bt + i * bt_stride (device,
  * bt_stride >= ceil(max_seq_len / page)); q and out are [nseq][H][D]. One slice pass
- * and one combine serve all sequences, and every sequence is cut exactly as a
- * single-sequence call of its length would be: out[i] is bit-identical to
- * w4b_attn_flash_w4_paged on sequence i. p->S is ignored. Served for D = 64 / 128,
+ * and one combine serve all sequences. For pages that are a power of two >= 16, eight
+ * consecutive sequences of equal length ride one CTA, and a 16-position block whose
+ * page is the same in all their tables (a shared prefix) is loaded and decoded once
+ * for the eight - nothing has to be declared, the tables are compared. out[i] is the
+ * same computation as w4b_attn_flash_w4_paged on sequence i (same kernels, same
+ * rel L2 <= 1e-3 against the FP64 reference) with the sequence cut into slices for
+ * ceil(nseq / 8) * H rows instead of H, so the bits agree when nseq == 1; they depend
+ * on nseq and the sequence's own length only, never on the other sequences of the
+ * call. p->S is ignored. Served for D = 64 / 128,
  * gs = 32 / 64 / 128 and 16-byte aligned caches and q; other shapes return
  * W4B_INVALID (call the per-sequence entry). seq_lens and bt contents are not
  * validated. */

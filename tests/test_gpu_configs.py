@@ -227,9 +227,10 @@ def test_c5_paged_geometry_two_sequences(oracle):
 
 
 def test_batched_paged_matches_per_sequence_calls(oracle):
-    """The batched paged entry: sequences of different lengths over one pool (two of them share prefix pages),
-    one launch; every sequence's output must carry the bits of the per-sequence entry, which is checked
-    against the FP64 reference."""
+    """The batched paged entry: sequences of different lengths over one pool (all prefixes of one another),
+    one launch; every sequence's output must match the FP64 reference and the per-sequence entry (the two cut
+    a sequence into different slices, so they agree to rounding, not to the bit), must not depend on the
+    company it has in the call, and a call with one sequence must carry the bits of the per-sequence entry."""
     H, D, gs, page = 4, 128, 32, 16
     lens = [4608, 300, 4100, 16, 1]
     rng = np.random.default_rng(21)
@@ -274,10 +275,104 @@ def test_batched_paged_matches_per_sequence_calls(oracle):
         out_1 = empty_f16(H * D)
         w4.attention_w4_flash_paged(d_i, ptr(bt_d) + 4 * i * stride, page, npages, ptr(q_d) + 2 * i * H * D, ptr(out_1))
         sync_ok()
-        assert np.array_equal(bits(out_1), got[i]), f"sequence {i} (length {L})"
         ref = oracle.attention_reference(qs[i * H * D:(i + 1) * H * D], np.ascontiguousarray(kd[:, :L]).ravel(),
                                          np.ascontiguousarray(vd[:, :L]).ravel(), H, L, D)
         assert cases.rel_l2(cases.f16(got[i]), ref) <= TOL, f"sequence {i}"
+        assert cases.rel_l2(cases.f16(got[i]), cases.f16(bits(out_1))) <= TOL, f"sequence {i} (length {L})"
+        # one sequence per batched call: the single-sequence geometry, hence its bits
+        out_s = empty_f16(H * D)
+        w4.attention_w4_flash_paged_batched(d_i, ptr(bt_d) + 4 * i * stride, stride, ptr(lens_d) + 4 * i, 1, L, page, npages,
+                                            ptr(q_d) + 2 * i * H * D, ptr(out_s))
+        sync_ok()
+        assert np.array_equal(bits(out_s), bits(out_1)), f"sequence {i} alone"
+    # the same sequences in another order and company: every output keeps its bits
+    order = [2, 0, 4, 1, 3]
+    bt2, lens2 = dev(bt[order].ravel()), dev(np.array([lens[i] for i in order], dtype=np.int32))
+    q2 = dev(qs.reshape(nseq, H * D)[order].ravel())
+    out_2 = empty_f16(nseq * H * D)
+    w4.attention_w4_flash_paged_batched(desc, ptr(bt2), stride, ptr(lens2), nseq, Smax, page, npages, ptr(q2), ptr(out_2))
+    sync_ok()
+    got2 = bits(out_2).reshape(nseq, H * D)
+    for j, i in enumerate(order):
+        assert np.array_equal(got2[j], got[i]), f"sequence {i} moved to slot {j}"
+
+
+@pytest.mark.parametrize("sym", [True, False])
+@pytest.mark.parametrize("D,gs", [(128, 32), (64, 64)])
+def test_batched_paged_shared_prefix_groups(oracle, D, gs, sym):
+    """Sequences of equal length that share prefix pages and then own pages (config 5's geometry, scaled down),
+    more than eight of them so that a full and a partial group of eight form: the batched entry decodes shared
+    blocks once per group; every sequence must match the FP64 reference and its single-sequence call, and must
+    carry the bits it gets when the same call serves it without sharing (a pool in which every sequence has
+    pages of its own). The length is not a multiple of the page."""
+    H, page, nseq = 3, 16, 11
+    n_pre, n_own = 21, 5
+    S = (n_pre + n_own) * page - 7
+    rng = np.random.default_rng(31 + D)
+    k_pre, v_pre = rng.standard_normal((H, n_pre * page, D)), rng.standard_normal((H, n_pre * page, D))
+    npages = n_pre + nseq * n_own + 4
+    perm = np.random.default_rng(32).permutation(npages).astype(np.int32)
+    lp = n_pre + n_own
+    wd, G = D // 8, D // gs
+    rows = npages * page
+    names = ("q_k", "q_v", "s_k", "s_v") + (() if sym else ("z_k", "z_v"))
+    width = {"q_k": wd, "q_v": wd, "s_k": G, "s_v": G, "z_k": 1, "z_v": 1}
+    pool, caches = {}, []
+    bt = np.zeros((nseq, lp), dtype=np.int32)
+    for i in range(nseq):
+        k_i = np.concatenate([k_pre, rng.standard_normal((H, lp * page - n_pre * page, D))], axis=1)[:, :S]
+        v_i = np.concatenate([v_pre, rng.standard_normal((H, lp * page - n_pre * page, D))], axis=1)[:, :S]
+        c = oracle.quantize_cache_w4(np.ascontiguousarray(k_i).ravel(), np.ascontiguousarray(v_i).ravel(), H, S, D, gs, sym)
+        caches.append(c)
+        bt[i, :n_pre] = perm[:n_pre]
+        bt[i, n_pre:] = perm[n_pre + i * n_own: n_pre + (i + 1) * n_own]
+        for n in names:
+            if n not in pool:
+                pool[n] = np.zeros((H, rows, width[n]), dtype=c[n].dtype)
+            src = np.zeros((H, lp * page, width[n]), dtype=c[n].dtype)
+            src[:, :S] = c[n].reshape(H, S, width[n])
+            for j, phys in enumerate(bt[i]):
+                if i == 0 or j >= n_pre:
+                    pool[n][:, phys * page:(phys + 1) * page] = src[:, j * page:(j + 1) * page]
+    t = {n: dev(np.ascontiguousarray(pool[n]).ravel()) for n in names}
+    zk, zv = (None, None) if sym else (ptr(t["z_k"]), ptr(t["z_v"]))
+    desc = w4.DeviceKVW4(H, S, D, gs, G, int(sym), ptr(t["q_k"]), ptr(t["s_k"]), zk, ptr(t["q_v"]), ptr(t["s_v"]), zv)
+    qs = oracle.normal_f16(nseq * H * D, 33)
+    q_d, bt_d, lens_d = dev(qs), dev(bt.ravel()), dev(np.full(nseq, S, dtype=np.int32))
+    out_b = empty_f16(nseq * H * D)
+    out_b.fill_(float("nan"))
+    w4.attention_w4_flash_paged_batched(desc, ptr(bt_d), lp, ptr(lens_d), nseq, S, page, npages, ptr(q_d), ptr(out_b))
+    sync_ok()
+    got = bits(out_b).reshape(nseq, H * D)
+    for i in range(nseq):
+        out_1 = empty_f16(H * D)
+        w4.attention_w4_flash_paged(desc, ptr(bt_d) + 4 * i * lp, page, npages, ptr(q_d) + 2 * i * H * D, ptr(out_1))
+        sync_ok()
+        assert cases.rel_l2(cases.f16(got[i]), cases.f16(bits(out_1))) <= TOL, f"sequence {i}"
+        if i in (0, 7, 10):
+            c = caches[i]
+            ref = oracle.attention_reference(qs[i * H * D:(i + 1) * H * D], oracle.dequant_cache_w4(c, "k"),
+                                             oracle.dequant_cache_w4(c, "v"), H, S, D)
+            assert cases.rel_l2(cases.f16(got[i]), ref) <= TOL, f"sequence {i}"
+    # the same sequences without sharing: prefix pages copied per sequence into a larger pool, so that every block
+    # runs once per sequence. Same slices, same order of sums: the bits must agree with the shared run.
+    npages2 = nseq * lp
+    rows2 = npages2 * page
+    bt_own = np.arange(npages2, dtype=np.int32).reshape(nseq, lp)
+    pool2 = {n: np.zeros((H, rows2, width[n]), dtype=pool[n].dtype) for n in names}
+    for i in range(nseq):
+        for j in range(lp):
+            src, dst = int(bt[i, j]), int(bt_own[i, j])
+            for n in names:
+                pool2[n][:, dst * page:(dst + 1) * page] = pool[n][:, src * page:(src + 1) * page]
+    t2 = {n: dev(np.ascontiguousarray(pool2[n]).ravel()) for n in names}
+    zk2, zv2 = (None, None) if sym else (ptr(t2["z_k"]), ptr(t2["z_v"]))
+    desc2 = w4.DeviceKVW4(H, S, D, gs, G, int(sym), ptr(t2["q_k"]), ptr(t2["s_k"]), zk2, ptr(t2["q_v"]), ptr(t2["s_v"]), zv2)
+    bt_own_d = dev(bt_own.ravel())
+    out_o = empty_f16(nseq * H * D)
+    w4.attention_w4_flash_paged_batched(desc2, ptr(bt_own_d), lp, ptr(lens_d), nseq, S, page, npages2, ptr(q_d), ptr(out_o))
+    sync_ok()
+    assert np.array_equal(bits(out_o).reshape(nseq, H * D), got)
 
 
 def test_peer_allgather_loopback():

@@ -256,7 +256,8 @@ def attention_w4_flash_paged(p: DeviceKVW4, bt, page, npages, q, out, stream=Non
 def attention_w4_flash_paged_batched(p: DeviceKVW4, bt, bt_stride, seq_lens, nseq, max_seq_len, page, npages, q, out,
                                      stream=None):
     """nseq sequences over one pool in one launch (no reference counterpart: its paged entry takes one
-    sequence per call); out[i] carries the bits of attention_w4_flash_paged on sequence i."""
+    sequence per call). Blocks whose page is common to eight consecutive sequences of equal length are
+    decoded once for the eight; out[i] is attention_w4_flash_paged on sequence i up to the order of the sums."""
     _check(lib.w4b_attn_flash_w4_paged_batched(C.byref(p._c()), bt, bt_stride, seq_lens, nseq, max_seq_len, page, npages,
                                                q, out, stream))
 

@@ -250,7 +250,7 @@ __global__ void flash_combine_kernel(const float* __restrict__ ws, __half* __res
                                      const int* __restrict__ seq_lens, int H, int sm_count) {
   const int h = blockIdx.x;
   const float* hb = ws + (size_t)h * splits * (size_t)(D + 2);
-  if (seq_lens) splits = attn_flash_splits(H, __ldg(seq_lens + h / H), sm_count);
+  if (seq_lens) splits = attn_flash_splits(attn_batched_rows((int)gridDim.x / H, H), __ldg(seq_lens + h / H), sm_count);
   if (splits == 1 && seq_lens) return;  // the slice pass wrote the output itself
   float mx = -CUDART_INF_F;
   for (int s = 0; s < splits; ++s) mx = fmaxf(mx, hb[(size_t)s * (D + 2)]);
@@ -332,8 +332,9 @@ cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* ou
 }
 
 // Batched paged decode attention: nseq sequences over one pool, one slice pass and one combine for all of them.
-// Every sequence is cut exactly as a single-sequence call of its length would be, so its output carries the same
-// bits. `max_splits` = attn_flash_splits(H, longest sequence, sm_count); ws holds nseq * H * max_splits partials.
+// A sequence of length S is cut into attn_flash_splits(attn_batched_rows(nseq, H), S, sm_count) slices (a function of
+// its own length only, so the result does not depend on which sequences share the call with it); `max_splits` is
+// that of the longest sequence and ws holds nseq * H * max_splits partials.
 cudaError_t attn_flash_batched_launch(const AttnSource& src, const __half* q, __half* out, int H, int D, int nseq,
                                       const int* seq_lens, int bt_stride, int max_splits, int sm_count, float* ws,
                                       cudaStream_t stream, int* launches) {

@@ -20,6 +20,14 @@
 //                  operation (two scales / zero points per instruction). No shared
 //                  memory, no transposes, every cache byte is loaded once.
 //
+// Batched paged form with shared pages (MULTI): a CTA serves up to eight sequences of one head at a time, sequence
+// j in column j of both products - B = the eight queries, resp. the eight weight vectors. A block whose page is
+// the same for all of them (a shared prefix) is loaded and decoded ONCE for the eight; a block with different
+// pages runs once per sequence with only that sequence's column live. Columns of an MMA are independent dot
+// products and a sequence's slices, block order and merge order depend on its own length only, so its output
+// does not depend on the company it has in the call (with one sequence per call: the bits of the
+// single-sequence entry); only the work is shared.
+//
 // Dequantised values are bit-identical to the host formats (the same decoders as
 // the GEMM kernels; FP8: the byte placed in a half is code * 2^-8, times 256 is
 // exact, times the scale rounds once). Sums are formed in a fixed order: lanes,
@@ -48,7 +56,7 @@ struct MmaParams {
   int gshift;  // log2(group size)
   int wide;    // the hooks may be written 16 bytes at a time
   // batched paged form: grid.x = nseq * H; sequence i has seq_lens[i] positions and the block table
-  // bt + i * bt_stride; its slices are those of a single-sequence call of that length
+  // bt + i * bt_stride; its slices are cut for attn_batched_rows(nseq, H) rows
   int nseq;             // 0: single sequence
   const int* seq_lens;  // device, nseq entries
   int bt_stride;
@@ -223,28 +231,32 @@ __device__ __forceinline__ void store8(__half* dst, uint4 v, bool wide) {
   }
 }
 
-template <int FMT, int D, bool HOOK>
+template <int FMT, int D, bool HOOK, bool MULTI>
 __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (FMT == ATTN_F8 ? 3 : 4)) attn_mma_kernel(const MmaParams p) {
   constexpr int E = D / 4;    // K elements per lane per row
   constexpr int EV = D / 8;   // V elements per lane per row
   constexpr int NQ = E / 8;   // q fragments (8 elements each) per lane
   constexpr int NT = EV / 2;  // output tiles (16 d each... per lane: rows g and g+8)
-  __shared__ float sm_ml[MA_WARPS][2];
-  __shared__ float sm_acc[MA_WARPS][D];
-  const int hx = blockIdx.x, sp = blockIdx.y;  // hx: row of q / out (sequence-major in the batched form)
-  const int h = p.nseq ? hx % p.H : hx;        // head: selects the slab
+  constexpr int COLS = MULTI ? 8 : 1;  // sequences per CTA (columns of the products that carry distinct data)
+  constexpr int NC = MULTI ? 2 : 1;    // columns whose softmax state a lane keeps (2c, 2c + 1)
+  __shared__ float sm_ml[MA_WARPS][COLS][2];
+  __shared__ float sm_acc[MA_WARPS][COLS][D];
+  // MULTI: the last slices first - those past a shared prefix run once per sequence and take the longest
+  const int sp = MULTI ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const int S = p.nseq ? __ldg(p.seq_lens + hx / p.H) : p.S;
-  const int splits = p.nseq ? attn_flash_splits(p.H, S, p.sm_count) : p.splits;
-  if (sp >= splits) return;  // (batched: the grid is sized for the longest sequence)
-  const int* bt = p.src.bt ? p.src.bt + (p.nseq ? (size_t)(hx / p.H) * p.bt_stride : 0) : nullptr;
-  // slices are cut at multiples of 64 positions: the four warps of a CTA get the same number of blocks
-  const int units = (S + MA_WARPS * MA_BLOCK - 1) / (MA_WARPS * MA_BLOCK);
-  const int t0 = MA_WARPS * MA_BLOCK * (int)((long long)units * sp / splits);
-  const int t1 = min(S, MA_WARPS * MA_BLOCK * (int)((long long)units * (sp + 1) / splits));
-  const float scale = rsqrtf((float)D);
   const AttnSource& s = p.src;
+  const W4Consts kc = w4_consts();
+  // MULTI: blockIdx.x = group * H + head, a group = eight consecutive sequences (fewer at the end). When their
+  // lengths are equal they share one pass; otherwise each sequence gets a pass of its own with one live column.
+  const int h = MULTI ? (int)(blockIdx.x % p.H) : (p.nseq ? (int)(blockIdx.x % p.H) : (int)blockIdx.x);
+  const int seq0 = MULTI ? 8 * (int)(blockIdx.x / p.H) : 0;
+  const int count = MULTI ? min(8, p.nseq - seq0) : 1;
+  int npass = 1, my_len = 0;
+  if constexpr (MULTI) {
+    my_len = __ldg(p.seq_lens + seq0 + min(lane, count - 1));
+    npass = __all_sync(0xffffffffu, my_len == __shfl_sync(0xffffffffu, my_len, 0)) ? 1 : count;
+  }
   HeadBase hb;
   {
     const size_t slab = (size_t)h * (size_t)s.slab_rows;
@@ -258,30 +270,50 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
     hb.zk = s.z_k ? s.z_k + slab * hb.wG : nullptr;
     hb.zv = s.z_v ? s.z_v + slab * hb.wG : nullptr;
   }
+  const float scale = rsqrtf((float)D);
 
-  // q of this lane's K quarter, in the pairing its K fragments use
+#pragma unroll 1
+  for (int pass = 0; pass < npass; ++pass) {
+  // live columns of this pass, the sequence whose geometry it uses, and the row of q / out of column 0
+  const uint32_t colmask = MULTI ? (npass == 1 ? (1u << count) - 1u : 1u << pass) : 1u;
+  const int firstcol = MULTI ? (npass == 1 ? 0 : pass) : 0;
+  const int hx = MULTI ? (seq0 * p.H + h) : (int)blockIdx.x;  // hx: row of q / out (sequence-major in the batched form)
+  const int S = MULTI ? __shfl_sync(0xffffffffu, my_len, firstcol) : (p.nseq ? __ldg(p.seq_lens + hx / p.H) : p.S);
+  const int splits = p.nseq ? attn_flash_splits(attn_batched_rows(p.nseq, p.H), S, p.sm_count) : p.splits;
+  if (sp >= splits) continue;  // (batched: the grid is sized for the longest sequence)
+  const int* bt = p.src.bt ? p.src.bt + (p.nseq ? (size_t)(MULTI ? seq0 : hx / p.H) * p.bt_stride : 0) : nullptr;
+  // slices are cut at multiples of 64 positions: the four warps of a CTA get the same number of blocks
+  const int units = (S + MA_WARPS * MA_BLOCK - 1) / (MA_WARPS * MA_BLOCK);
+  const int t0 = MA_WARPS * MA_BLOCK * (int)((long long)units * sp / splits);
+  const int t1 = min(S, MA_WARPS * MA_BLOCK * (int)((long long)units * (sp + 1) / splits));
+  // q of this lane's K quarter, in the pairing its K fragments use (MULTI: the query of sequence g, column g)
   uint4 qf[NQ];
 #pragma unroll
   for (int i = 0; i < NQ; ++i) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q + (size_t)hx * D + E * c) + i);
+    const size_t qrow = MULTI ? (size_t)hx + (size_t)min(g, count - 1) * p.H : (size_t)hx;
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.q + qrow * D + E * c) + i);
     qf[i] = (FMT == ATTN_W4_SYM || FMT == ATTN_W4_ASYM) ? pair_permute(v) : v;
   }
 
-  float m = -CUDART_INF_F, l = 0.0f;
+  float m[NC], l[NC];
+#pragma unroll
+  for (int x = 0; x < NC; ++x) m[x] = -CUDART_INF_F, l[x] = 0.0f;
   float acc[NT][4];
 #pragma unroll
   for (int j = 0; j < NT; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
-  const W4Consts kc = w4_consts();
 
-  auto fetch = [&](BlockData<FMT, D>& blk, int tb) {
+  auto fetch = [&](BlockData<FMT, D>& blk, int tb, int page_id) {
     const int last = t1 - 1;  // positions past the slice read a valid row and get weight 0
     int rk[2], rv[4];
-    if (bt == nullptr || p.pshift >= 0) {
+    if (MULTI || bt == nullptr || p.pshift >= 0) {
       // contiguous cache, or pages that are a power of two >= 16: the block's 16 positions (tb is a multiple of
-      // 16) lie in one page, so one table entry serves the block
-      const int base = bt == nullptr ? tb : (__ldg(bt + (tb >> p.pshift)) << p.pshift) + (tb & ((1 << p.pshift) - 1));
+      // 16) lie in one page, so one table entry serves the block (MULTI: the caller has looked it up)
+      // (MULTI: a table entry outside the pool is clamped rather than followed)
+      const int pg = MULTI ? min(max(page_id, 0), (int)(s.slab_rows >> p.pshift) - 1)
+                           : (bt == nullptr ? 0 : __ldg(bt + (tb >> p.pshift)));
+      const int base = bt == nullptr ? tb : (pg << p.pshift) + (tb & ((1 << p.pshift) - 1));
       const int lim = last - tb;
       rk[0] = base + min(g, lim);
       rk[1] = base + min(g + 8, lim);
@@ -301,7 +333,8 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
     blk.load(hb, rk, rv, g, c, p.gshift);
   };
 
-  auto compute = [&](const BlockData<FMT, D>& cur, int tb) {
+  // ucol: MULTI only - the one live column of this item, or -1 for every column of the pass
+  auto compute = [&](const BlockData<FMT, D>& cur, int tb, int ucol) {
 
     // ---------------- scores of rows g and g + 8 ----------------
     float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
@@ -357,6 +390,8 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
         mma_16816(sb, f1, qf[i].z, qf[i].w);
       }
     }
+    uint32_t pb0, pb1;
+    if constexpr (!MULTI) {
     // the MMA has summed the four lanes' quarters; every column of the product holds the score
     float s0 = sa[0] + sb[0], s1 = sa[2] + sb[2];
     s0 = (tb + g < t1) ? s0 * scale : -CUDART_INF_F;
@@ -371,27 +406,70 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
     // Written as a loop so that it stays a branch. Only columns 0 of the accumulators are
     // ever read (every column holds the same sums), so only those are rescaled.
 #pragma unroll 1
-    while (bm > m) {
-      const float corr = __expf(m - bm);  // m = -inf on the first block: 0
-      l *= corr;
+    while (bm > m[0]) {
+      const float corr = __expf(m[0] - bm);  // m = -inf on the first block: 0
+      l[0] *= corr;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         acc[j][0] *= corr;
         acc[j][2] *= corr;
       }
-      m = bm;
+      m[0] = bm;
     }
     // weights as FP16 (the MMA's input type); the denominator adds the same rounded values
-    const __half2 pp = __floats2half2_rn(__expf(s0 - m), __expf(s1 - m));  // (p[g], p[g+8])
+    const __half2 pp = __floats2half2_rn(__expf(s0 - m[0]), __expf(s1 - m[0]));  // (p[g], p[g+8])
     float ps = __low2float(pp) + __high2float(pp);
     ps += __shfl_xor_sync(0xffffffffu, ps, 4);
     ps += __shfl_xor_sync(0xffffffffu, ps, 8);
     ps += __shfl_xor_sync(0xffffffffu, ps, 16);
-    l += ps;
+    l[0] += ps;
     const uint32_t pu = __shfl_sync(0xffffffffu, h2_as_u32(pp), 8 * c);      // positions 2c, 2c+8
     const uint32_t pv = __shfl_sync(0xffffffffu, h2_as_u32(pp), 8 * c + 4);  // positions 2c+1, 2c+9
-    const uint32_t pb0 = __byte_perm(pu, pv, 0x5410);                        // (p[2c], p[2c+1])
-    const uint32_t pb1 = __byte_perm(pu, pv, 0x7632);                        // (p[2c+8], p[2c+9])
+    pb0 = __byte_perm(pu, pv, 0x5410);                                       // (p[2c], p[2c+1])
+    pb1 = __byte_perm(pu, pv, 0x7632);                                       // (p[2c+8], p[2c+9])
+    } else {
+    // Column n of the product is sequence n: this lane holds the scores of positions g, g + 8 for the
+    // sequences 2c and 2c + 1. Each column runs the single-sequence arithmetic above on its own values.
+    uint32_t ppu[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const int col = 2 * c + x;
+      const bool live = ucol < 0 ? ((colmask >> col) & 1u) != 0 : col == ucol;
+      float s0 = sa[x] + sb[x], s1 = sa[2 + x] + sb[2 + x];
+      s0 = (live && tb + g < t1) ? s0 * scale : -CUDART_INF_F;
+      s1 = (live && tb + g + 8 < t1) ? s1 * scale : -CUDART_INF_F;
+      float bm = fmaxf(s0, s1);
+      bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+      bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
+      bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
+      if (bm > m[x]) {
+        const float corr = __expf(m[x] - bm);
+        l[x] *= corr;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          acc[j][x] *= corr;
+          acc[j][2 + x] *= corr;
+        }
+        m[x] = bm;
+      }
+      // a column that is not live gets weight 0 (its maximum may still be -inf)
+      const __half2 pp = live ? __floats2half2_rn(__expf(s0 - m[x]), __expf(s1 - m[x])) : __floats2half2_rn(0.0f, 0.0f);
+      float ps = __low2float(pp) + __high2float(pp);
+      ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+      ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+      ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+      l[x] += ps;
+      ppu[x] = h2_as_u32(pp);
+    }
+    // B of the second product: this lane needs positions 2c, 2c+1, 2c+8, 2c+9 of sequence g; the lanes
+    // (2c, g / 2) and (2c + 1, g / 2) hold them in their column g % 2
+    const int src = 8 * c + (g >> 1);
+    const uint32_t u0 = __shfl_sync(0xffffffffu, ppu[0], src), u1 = __shfl_sync(0xffffffffu, ppu[1], src);
+    const uint32_t v0 = __shfl_sync(0xffffffffu, ppu[0], src + 4), v1 = __shfl_sync(0xffffffffu, ppu[1], src + 4);
+    const uint32_t pu = (g & 1) ? u1 : u0, pv = (g & 1) ? v1 : v0;
+    pb0 = __byte_perm(pu, pv, 0x5410);
+    pb1 = __byte_perm(pu, pv, 0x7632);
+    }
 
     // ---------------- V^T fragments: element e of rows (2c, 2c+1) and of rows (2c+8, 2c+9) ----------------
     uint32_t v12[EV], v34[EV];
@@ -481,35 +559,98 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   const int step = MA_WARPS * MA_BLOCK;
   int tb = t0 + wid * MA_BLOCK;
   BlockData<FMT, D> bufa, bufb;
-  if (tb < t1) fetch(bufa, tb);
-  while (tb < t1) {
-    if (tb + step < t1) fetch(bufb, tb + step);
-    compute(bufa, tb);
-    tb += step;
-    if (tb >= t1) break;
-    if (tb + step < t1) fetch(bufa, tb + step);
-    compute(bufb, tb);
-    tb += step;
+  if constexpr (!MULTI) {
+    if (tb < t1) fetch(bufa, tb, 0);
+    while (tb < t1) {
+      if (tb + step < t1) fetch(bufb, tb + step, 0);
+      compute(bufa, tb, -1);
+      tb += step;
+      if (tb >= t1) break;
+      if (tb + step < t1) fetch(bufa, tb + step, 0);
+      compute(bufb, tb, -1);
+      tb += step;
+    }
+  } else {
+    // Items: a block whose page is common to the live sequences is one item for all columns (ucol = -1);
+    // otherwise one item per live sequence. Lane j keeps the page of sequence j for the block at hand.
+    int pages = 0;
+    auto classify = [&](int t) -> int {  // loads the block's pages; returns the first item's column
+      pages = __ldg(bt + (size_t)min(lane, count - 1) * p.bt_stride + (t >> p.pshift));
+      const int first = __shfl_sync(0xffffffffu, pages, firstcol);  // (every lane takes part in the shuffle)
+      const bool same = !((colmask >> lane) & 1u) || pages == first;
+      return __all_sync(0xffffffffu, same) ? -1 : firstcol;
+    };
+    // the item after (t, u): false when the slice is done
+    auto advance = [&](int& t, int& u) -> bool {
+      if (u >= 0) {
+        const uint32_t rest = colmask >> (u + 1);
+        if (rest) {
+          u += __ffs(rest);
+          return true;
+        }
+      }
+      t += step;
+      if (t >= t1) return false;
+      u = classify(t);
+      return true;
+    };
+    auto page_of = [&](int u) { return __shfl_sync(0xffffffffu, pages, u < 0 ? firstcol : u); };
+    int ucur = 0;
+    bool have = tb < t1;
+    if (have) {
+      ucur = classify(tb);
+      fetch(bufa, tb, page_of(ucur));
+    }
+    while (have) {
+      int tn = tb, un = ucur;
+      have = advance(tn, un);
+      if (have) fetch(bufb, tn, page_of(un));
+      compute(bufa, tb, ucur);
+      if (!have) break;
+      tb = tn, ucur = un;
+      have = advance(tn, un);
+      if (have) fetch(bufa, tn, page_of(un));
+      compute(bufb, tb, ucur);
+      tb = tn, ucur = un;
+    }
   }
 
-  // ---- warps of the CTA, merged in warp order; every column of acc holds the same value ----
-  if (lane == 0) {
-    sm_ml[wid][0] = m;
-    sm_ml[wid][1] = l;
-  }
-  if (c == 0) {
+  // ---- warps of the CTA, merged in warp order (single form: every column of acc holds the same value) ----
+  if (pass > 0) __syncthreads();  // the previous pass's readers are done
+  if constexpr (!MULTI) {
+    if (lane == 0) {
+      sm_ml[wid][0][0] = m[0];
+      sm_ml[wid][0][1] = l[0];
+    }
+    if (c == 0) {
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      sm_acc[wid][EV * g + j] = acc[j][0];
-      sm_acc[wid][EV * g + NT + j] = acc[j][2];
+      for (int j = 0; j < NT; ++j) {
+        sm_acc[wid][0][EV * g + j] = acc[j][0];
+        sm_acc[wid][0][EV * g + NT + j] = acc[j][2];
+      }
+    }
+  } else {
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      if (g == 0) {
+        sm_ml[wid][2 * c + x][0] = m[x];
+        sm_ml[wid][2 * c + x][1] = l[x];
+      }
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        sm_acc[wid][2 * c + x][EV * g + j] = acc[j][x];
+        sm_acc[wid][2 * c + x][EV * g + NT + j] = acc[j][2 + x];
+      }
     }
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < D; d += MA_THREADS) {
-    float mm = sm_ml[0][0], ll = sm_ml[0][1], a = sm_acc[0][d];
+  for (int idx = threadIdx.x; idx < COLS * D; idx += MA_THREADS) {
+    const int col = idx / D, d = idx - col * D;
+    if (MULTI && !((colmask >> col) & 1u)) continue;
+    float mm = sm_ml[0][col][0], ll = sm_ml[0][col][1], a = sm_acc[0][col][d];
 #pragma unroll
     for (int w = 1; w < MA_WARPS; ++w) {
-      const float m2 = sm_ml[w][0], l2 = sm_ml[w][1], a2 = sm_acc[w][d];
+      const float m2 = sm_ml[w][col][0], l2 = sm_ml[w][col][1], a2 = sm_acc[w][col][d];
       const float mn = fmaxf(mm, m2);
       const float fa = (mm == -CUDART_INF_F) ? 0.0f : __expf(mm - mn);
       const float fb = (m2 == -CUDART_INF_F) ? 0.0f : __expf(m2 - mn);
@@ -517,10 +658,11 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       a = a * fa + a2 * fb;
       mm = mn;
     }
+    const size_t row = (size_t)hx + (size_t)col * p.H;  // (col is 0 in the single form)
     if (splits == 1) {
-      p.out[(size_t)hx * D + d] = __float2half_rn(a / ll);
+      p.out[row * D + d] = __float2half_rn(a / ll);
     } else {
-      float* part = p.ws + ((size_t)hx * (p.nseq ? p.splits : splits) + sp) * (size_t)(D + 2);
+      float* part = p.ws + (row * (p.nseq ? p.splits : splits) + sp) * (size_t)(D + 2);
       if (d == 0) {
         part[0] = mm;
         part[1] = ll;
@@ -528,15 +670,23 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       part[2 + d] = a;
     }
   }
+  }  // pass
 }
 
 template <int FMT, int D>
 cudaError_t launch_d(const MmaParams& p, cudaStream_t stream) {
   const dim3 grid((unsigned)(p.nseq ? p.nseq * p.H : p.H), (unsigned)p.splits);
+  if constexpr (FMT == ATTN_W4_SYM || FMT == ATTN_W4_ASYM) {
+    if (p.nseq > 1 && p.pshift >= 0) {  // sequences of one pool, eight to a CTA: shared pages are decoded once
+      const dim3 ggrid((unsigned)(((p.nseq + 7) / 8) * p.H), (unsigned)p.splits);
+      attn_mma_kernel<FMT, D, false, true><<<ggrid, MA_THREADS, 0, stream>>>(p);
+      return cudaGetLastError();
+    }
+  }
   if (p.k_out || p.v_out)
-    attn_mma_kernel<FMT, D, true><<<grid, MA_THREADS, 0, stream>>>(p);
+    attn_mma_kernel<FMT, D, true, false><<<grid, MA_THREADS, 0, stream>>>(p);
   else
-    attn_mma_kernel<FMT, D, false><<<grid, MA_THREADS, 0, stream>>>(p);
+    attn_mma_kernel<FMT, D, false, false><<<grid, MA_THREADS, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

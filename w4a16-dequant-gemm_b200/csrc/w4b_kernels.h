@@ -127,6 +127,9 @@ __host__ __device__ inline int attn_flash_splits(int H, int S, int sm_count) {
   if (want < 1) want = 1;
   return (int)want;
 }
+// The batched paged form serves eight sequences of a head per CTA, so it cuts every sequence's slices for
+// ceil(nseq / 8) * H independent rows (a single sequence: H, the geometry of the single-sequence entry).
+__host__ __device__ inline int attn_batched_rows(int nseq, int H) { return ((nseq + 7) / 8) * H; }
 size_t attn_flash_ws_bytes(int H, int D, int splits);
 cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
                               float* ws, __half* k_out, __half* v_out, cudaStream_t stream, int* launches);
