@@ -208,6 +208,84 @@ struct BlockData<ATTN_W4_SYM, D> : BlockDataW4<ATTN_W4_SYM, D> {};
 template <int D>
 struct BlockData<ATTN_W4_ASYM, D> : BlockDataW4<ATTN_W4_ASYM, D> {};
 
+// W4 block of the single-sequence form, whose products take the scales OUT of the contraction (see the kernel):
+// the same words, but the K scales of the two quarters whose partial scores this lane finishes (quarters 2c and
+// 2c + 1 of rows g and g + 8; lanes c >= 2 finish nothing and load what lanes c - 2 load) and the V scales of the
+// group that is this lane's COLUMN of the second product (group g; none for g >= G). With hooks the scales of
+// the lane's own words come along for the exact decode.
+template <int FMT, int D, bool HOOK>
+struct BlockDataW4Fold {
+  static constexpr int KW = D / 32, VW = D / 64, WD = D / 8, E = D / 4;
+  uint32_t k[2][KW];
+  uint32_t v[4][VW];
+  __half ks[2][2], vs[4];
+  uint32_t kz[2][2], vz[4];
+  __half ks_own[HOOK ? 2 : 1], vs_own[HOOK ? 4 : 1];
+  uint32_t kz_own[HOOK ? 2 : 1];
+  __device__ __forceinline__ static uint32_t zero_of(const uint32_t* z, int row, int wG, int grp) {
+    return FMT == ATTN_W4_ASYM ? ((__ldg(z + (size_t)(unsigned)(row * wG + (grp >> 3))) >> (4 * (grp & 7))) & 0xFu) : 8u;
+  }
+  __device__ __forceinline__ void load(const HeadBase& s, const int rk[2], const int rv[4], int g, int c, int gshift) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(s.k + (size_t)(unsigned)rk[r] * (WD * 4)) + KW * c;
+      if (KW == 4) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+        k[r][0] = a.x, k[r][1] = a.y, k[r][2 % KW] = a.z, k[r][3 % KW] = a.w;
+      } else {
+        const uint2 a = __ldg(reinterpret_cast<const uint2*>(p));
+        k[r][0] = a.x, k[r][1] = a.y;
+      }
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        const int grp = (E * ((2 * c + x) & 3)) >> gshift;
+        ks[r][x] = ldg_half(s.sk + (size_t)(unsigned)(rk[r] * s.G + grp));
+        kz[r][x] = zero_of(s.zk, rk[r], s.wG, grp);
+      }
+      if (HOOK) {
+        const int grp = (E * c) >> gshift;
+        ks_own[r % (HOOK ? 2 : 1)] = ldg_half(s.sk + (size_t)(unsigned)(rk[r] * s.G + grp));
+        kz_own[r % (HOOK ? 2 : 1)] = zero_of(s.zk, rk[r], s.wG, grp);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(s.v + (size_t)(unsigned)rv[r] * (WD * 4)) + VW * g;
+      if (VW == 2) {
+        const uint2 a = __ldg(reinterpret_cast<const uint2*>(p));
+        v[r][0] = a.x, v[r][1 % VW] = a.y;
+      } else {
+        v[r][0] = __ldg(p);
+      }
+      const int col = min(g, s.G - 1);
+      const int grp = ((D / 8) * g) >> gshift;  // the group of this lane's own rows of V^T
+      vs[r] = ldg_half(s.sv + (size_t)(unsigned)(rv[r] * s.G + col));
+      vz[r] = zero_of(s.zv, rv[r], s.wG, grp);
+      if (HOOK) vs_own[r % (HOOK ? 4 : 1)] = ldg_half(s.sv + (size_t)(unsigned)(rv[r] * s.G + grp));
+    }
+  }
+};
+
+template <int FMT, int D, bool FOLD, bool HOOK>
+struct BlockSel {
+  using type = BlockData<FMT, D>;
+};
+template <int FMT, int D, bool HOOK>
+struct BlockSel<FMT, D, true, HOOK> {
+  using type = BlockDataW4Fold<FMT, D, HOOK>;
+};
+
+// The eight codes of a packed word as FP16 bit patterns, no arithmetic: out[0] = codes (0, 4) and out[2] = codes
+// (2, 6) are code * 2^-24 (a code in the low nibble of a half is that subnormal), out[1] = codes (1, 5) and
+// out[3] = codes (3, 7) are code * 2^-20 (the nibble above). 1 shift + 4 AND.
+__device__ __forceinline__ void w4_raw_codes(uint32_t qw, const W4Consts& k, uint32_t out[4]) {
+  const uint32_t hi = qw >> 8;
+  out[0] = qw & k.lo;
+  out[1] = qw & k.hi;
+  out[2] = hi & k.lo;
+  out[3] = hi & k.hi;
+}
+
 __device__ __forceinline__ uint4 unpair4(const __half2 p[4]) {  // (e, e+4) pairs -> 8 halves in order
   uint4 r;
   r.x = __byte_perm(h2_as_u32(p[0]), h2_as_u32(p[1]), 0x5410);
@@ -237,6 +315,17 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   constexpr int EV = D / 8;   // V elements per lane per row
   constexpr int NQ = E / 8;   // q fragments (8 elements each) per lane
   constexpr int NT = EV / 2;  // output tiles (16 d each... per lane: rows g and g+8)
+  constexpr bool IS_W4 = FMT == ATTN_W4_SYM || FMT == ATTN_W4_ASYM;
+  // Single-sequence W4: the scales are taken out of both contractions. The A operands are the raw codes (exact
+  // FP16 subnormals, five instructions per word instead of thirteen) and the spare columns of the products keep
+  // apart what needs different scales: in scores = K q, B holds q in column n only for the k slots of lane n, so
+  // column n is the partial score of quarter n of the head dimension and is scaled afterwards in FP32
+  // (s * (2^24 * sum - z * sum of q)); in out^T = V^T p, column n of B is p * scale of group n (rounded to FP16 as
+  // p alone was), row d reads its own group's column, and one more MMA with an all-ones A gives the sums that
+  // carry the zero points. With hooks the same arithmetic runs and the exact decode is done beside it for the
+  // stores, so the output bits do not depend on the hooks. (MULTI needs the columns for the sequences.)
+  constexpr bool FOLD = IS_W4 && !MULTI;
+  using Blk = typename BlockSel<FMT, D, FOLD, HOOK>::type;
   constexpr int COLS = MULTI ? 8 : 1;  // sequences per CTA (columns of the products that carry distinct data)
   constexpr int NC = MULTI ? 2 : 1;    // columns whose softmax state a lane keeps (2c, 2c + 1)
   __shared__ float sm_ml[MA_WARPS][COLS][2];
@@ -295,6 +384,32 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
     qf[i] = (FMT == ATTN_W4_SYM || FMT == ATTN_W4_ASYM) ? pair_permute(v) : v;
   }
 
+  // FOLD: sums of q over the two quarters whose partial scores this lane finishes, times the symmetric zero
+  // point; q itself only in the column that is this lane's own quarter, the hi-nibble pairs divided by 16
+  float zq[2] = {0.0f, 0.0f};
+  float c1[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // FOLD: 2^-24 * sum over positions of p * scale * zero point, per column
+  if constexpr (FOLD) {
+    float qs = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+      const uint32_t w[4] = {qf[i].x, qf[i].y, qf[i].z, qf[i].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(u32_as_h2(w[e]));
+        qs += f.x + f.y;
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < 2; ++x) zq[x] = __shfl_sync(0xffffffffu, qs, (lane & ~3) | ((2 * c + x) & 3));
+    const __half2 sixteenth = u32_as_h2(0x2C002C00u);
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+      qf[i].y = h2_as_u32(__hmul2_rn(u32_as_h2(qf[i].y), sixteenth));
+      qf[i].w = h2_as_u32(__hmul2_rn(u32_as_h2(qf[i].w), sixteenth));
+      if (g != c) qf[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+
   float m[NC], l[NC];
 #pragma unroll
   for (int x = 0; x < NC; ++x) m[x] = -CUDART_INF_F, l[x] = 0.0f;
@@ -304,7 +419,7 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
-  auto fetch = [&](BlockData<FMT, D>& blk, int tb, int page_id) {
+  auto fetch = [&](Blk& blk, int tb, int page_id) {
     const int last = t1 - 1;  // positions past the slice read a valid row and get weight 0
     int rk[2], rv[4];
     if (MULTI || bt == nullptr || p.pshift >= 0) {
@@ -334,7 +449,30 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   };
 
   // ucol: MULTI only - the one live column of this item, or -1 for every column of the pass
-  auto compute = [&](const BlockData<FMT, D>& cur, int tb, int ucol) {
+  // Hook stores of four V rows from (row 2c | row 2c+1) and (row 2c+8 | row 2c+9) pairs of halves
+  auto store_v_rows_at = [&](const uint32_t* a12, const uint32_t* a34, int tb) {
+#pragma unroll
+      for (int e0 = 0; e0 < EV; e0 += 8) {
+        uint4 a, b, cc, d;
+        a.x = __byte_perm(a12[e0], a12[e0 + 1], 0x5410), a.y = __byte_perm(a12[e0 + 2], a12[e0 + 3], 0x5410);
+        a.z = __byte_perm(a12[e0 + 4], a12[e0 + 5], 0x5410), a.w = __byte_perm(a12[e0 + 6], a12[e0 + 7], 0x5410);
+        b.x = __byte_perm(a12[e0], a12[e0 + 1], 0x7632), b.y = __byte_perm(a12[e0 + 2], a12[e0 + 3], 0x7632);
+        b.z = __byte_perm(a12[e0 + 4], a12[e0 + 5], 0x7632), b.w = __byte_perm(a12[e0 + 6], a12[e0 + 7], 0x7632);
+        cc.x = __byte_perm(a34[e0], a34[e0 + 1], 0x5410), cc.y = __byte_perm(a34[e0 + 2], a34[e0 + 3], 0x5410);
+        cc.z = __byte_perm(a34[e0 + 4], a34[e0 + 5], 0x5410), cc.w = __byte_perm(a34[e0 + 6], a34[e0 + 7], 0x5410);
+        d.x = __byte_perm(a34[e0], a34[e0 + 1], 0x7632), d.y = __byte_perm(a34[e0 + 2], a34[e0 + 3], 0x7632);
+        d.z = __byte_perm(a34[e0 + 4], a34[e0 + 5], 0x7632), d.w = __byte_perm(a34[e0 + 6], a34[e0 + 7], 0x7632);
+        const int d0 = EV * g + e0;
+        const size_t base = ((size_t)h * p.S + tb) * D + d0;
+        if (tb + 2 * c < t1) store8(p.v_out + base + (size_t)(2 * c) * D, a, p.wide);
+        if (tb + 2 * c + 1 < t1) store8(p.v_out + base + (size_t)(2 * c + 1) * D, b, p.wide);
+        if (tb + 2 * c + 8 < t1) store8(p.v_out + base + (size_t)(2 * c + 8) * D, cc, p.wide);
+        if (tb + 2 * c + 9 < t1) store8(p.v_out + base + (size_t)(2 * c + 9) * D, d, p.wide);
+      }
+  };
+
+  auto compute = [&](const Blk& cur, int tb, int ucol) {
+    auto store_v_rows = [&](const uint32_t* a12, const uint32_t* a34) { store_v_rows_at(a12, a34, tb); };
 
     // ---------------- scores of rows g and g + 8 ----------------
     float sa[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
@@ -372,6 +510,41 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
         mma_16816(sa, f0, qf[i].x, qf[i].y);
         mma_16816(sb, f1, qf[i].z, qf[i].w);
       }
+    } else if constexpr (FOLD) {
+#pragma unroll
+      for (int i = 0; i < NQ; ++i) {
+        uint32_t a[4], b[4];
+        w4_raw_codes(cur.k[0][i], kc, a);
+        w4_raw_codes(cur.k[1][i], kc, b);
+        if (HOOK && p.k_out) {
+          __half2 ea[4], eb[4];
+          dq_w4_word(cur.k[0][i], w4_group(cur.ks_own[0], cur.kz_own[0]), kc, ea);
+          dq_w4_word(cur.k[1][i], w4_group(cur.ks_own[HOOK ? 1 : 0], cur.kz_own[HOOK ? 1 : 0]), kc, eb);
+          const int d0 = E * c + 8 * i;
+          if (tb + g < t1) store8(p.k_out + ((size_t)h * p.S + tb + g) * D + d0, unpair4(ea), p.wide);
+          if (tb + g + 8 < t1) store8(p.k_out + ((size_t)h * p.S + tb + g + 8) * D + d0, unpair4(eb), p.wide);
+        }
+        const uint32_t f0[4] = {a[0], b[0], a[1], b[1]};
+        const uint32_t f1[4] = {a[2], b[2], a[3], b[3]};
+        mma_16816(sa, f0, qf[i].x, qf[i].y);
+        mma_16816(sb, f1, qf[i].z, qf[i].w);
+      }
+      // columns 2c, 2c + 1 (c < 2) are the code sums of quarters 2c, 2c + 1: scale them, add the four quarters
+      // of a row within the quad, and leave the row's score in every column as the plain form does
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float part = 0.0f;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const float zt = FMT == ATTN_W4_ASYM ? (float)cur.kz[r][x] * zq[x] : 8.0f * zq[x];
+          part = fmaf(__half2float(cur.ks[r][x]), fmaf(sa[2 * r + x] + sb[2 * r + x], 16777216.0f, -zt), part);
+        }
+        part = c < 2 ? part : 0.0f;
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        sa[2 * r] = part;
+        sb[2 * r] = 0.0f;
+      }
     } else {
       const W4Group ga = w4_group(cur.ks[0], cur.kz[0]), gb = w4_group(cur.ks[1], cur.kz[1]);
 #pragma unroll
@@ -379,11 +552,6 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
         __half2 a[4], b[4];
         dq_w4_word(cur.k[0][i], ga, kc, a);
         dq_w4_word(cur.k[1][i], gb, kc, b);
-        if (HOOK && p.k_out) {
-          const int d0 = E * c + 8 * i;
-          if (tb + g < t1) store8(p.k_out + ((size_t)h * p.S + tb + g) * D + d0, unpair4(a), p.wide);
-          if (tb + g + 8 < t1) store8(p.k_out + ((size_t)h * p.S + tb + g + 8) * D + d0, unpair4(b), p.wide);
-        }
         const uint32_t f0[4] = {h2_as_u32(a[0]), h2_as_u32(b[0]), h2_as_u32(a[1]), h2_as_u32(b[1])};
         const uint32_t f1[4] = {h2_as_u32(a[2]), h2_as_u32(b[2]), h2_as_u32(a[3]), h2_as_u32(b[3])};
         mma_16816(sa, f0, qf[i].x, qf[i].y);
@@ -402,17 +570,27 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
     bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
-    // A new running maximum (the same decision in every lane; rare after the first blocks).
-    // Written as a loop so that it stays a branch. Only columns 0 of the accumulators are
-    // ever read (every column holds the same sums), so only those are rescaled.
+    // A new running maximum (the same decision in every lane; rare after the first blocks). Only columns 0 of
+    // the accumulators are ever read in the plain form (every column holds the same sums), so only those are
+    // rescaled there.
 #pragma unroll 1
-    while (bm > m[0]) {
+    // The trip count (0 or 1) comes out of a vote so that the compiler sees a loop and not an `if` it may turn into
+    // predicated multiplications that cost every block their issue slots.
+    for (int again = __popc(__ballot_sync(0xffffffffu, bm > m[0])) >> 5; again > 0; --again) {
       const float corr = __expf(m[0] - bm);  // m = -inf on the first block: 0
       l[0] *= corr;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         acc[j][0] *= corr;
         acc[j][2] *= corr;
+        if (FOLD) {  // (a row's sum sits in its group's column)
+          acc[j][1] *= corr;
+          acc[j][3] *= corr;
+        }
+      }
+      if (FOLD) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c1[i] *= corr;
       }
       m[0] = bm;
     }
@@ -500,18 +678,70 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
         v12[e] = h2_as_u32(dq_f8_pair(__byte_perm(cur.v[0][w], cur.v[1][w], sel), s12));
         v34[e] = h2_as_u32(dq_f8_pair(__byte_perm(cur.v[2][w], cur.v[3][w], sel), s34));
       }
+    } else if constexpr (FOLD) {
+      // B of this product: column g = p times the scale of group g (nothing for g >= G). The zero points ride a
+      // second A operand: rows d hold the zero point of their own group at each position (as the codes are held),
+      // so that column's sum is the exact counterpart of the code sums - same B, same products.
+      {
+        const bool live = g < hb.G;
+        __half2 s01 = __halves2half2(cur.vs[0], cur.vs[1]), s23 = __halves2half2(cur.vs[2], cur.vs[3]);
+        if (!live) s01 = s23 = u32_as_h2(0u);
+        pb0 = h2_as_u32(__hmul2_rn(u32_as_h2(pb0), s01));
+        pb1 = h2_as_u32(__hmul2_rn(u32_as_h2(pb1), s23));
+        const uint32_t za = cur.vz[0] | (cur.vz[1] << 16), zb = cur.vz[2] | (cur.vz[3] << 16);  // z * 2^-24
+        const uint32_t zf[4] = {za, za, zb, zb};
+        mma_16816(c1, zf, pb0, pb1);
+      }
+#pragma unroll
+      for (int w = 0; w < EV / 8; ++w) {
+        uint32_t lo[4], hi[4];
+        w4_raw_codes(__byte_perm(cur.v[0][w], cur.v[1][w], 0x5410), kc, lo);  // codes 0..3 of both rows
+        w4_raw_codes(__byte_perm(cur.v[0][w], cur.v[1][w], 0x7632), kc, hi);  // codes 4..7
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v12[8 * w + i] = lo[i];
+          v12[8 * w + 4 + i] = hi[i];
+        }
+        w4_raw_codes(__byte_perm(cur.v[2][w], cur.v[3][w], 0x5410), kc, lo);
+        w4_raw_codes(__byte_perm(cur.v[2][w], cur.v[3][w], 0x7632), kc, hi);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v34[8 * w + i] = lo[i];
+          v34[8 * w + 4 + i] = hi[i];
+        }
+      }
+      if (HOOK && p.v_out) {  // the exact values, for the stores only
+        const W4Group g12 = w4_group2(cur.vs_own[0], cur.vz[0], cur.vs_own[HOOK ? 1 : 0], cur.vz[1]);
+        const W4Group g34 = w4_group2(cur.vs_own[HOOK ? 2 : 0], cur.vz[2], cur.vs_own[HOOK ? 3 : 0], cur.vz[3]);
+        uint32_t e12[EV], e34[EV];
+#pragma unroll
+        for (int w = 0; w < EV / 8; ++w) {
+          __half2 lo[4], hi[4];
+          dq_w4_word(__byte_perm(cur.v[0][w], cur.v[1][w], 0x5410), g12, kc, lo);
+          dq_w4_word(__byte_perm(cur.v[0][w], cur.v[1][w], 0x7632), g12, kc, hi);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            e12[8 * w + i] = h2_as_u32(lo[i]);
+            e12[8 * w + 4 + i] = h2_as_u32(hi[i]);
+          }
+          dq_w4_word(__byte_perm(cur.v[2][w], cur.v[3][w], 0x5410), g34, kc, lo);
+          dq_w4_word(__byte_perm(cur.v[2][w], cur.v[3][w], 0x7632), g34, kc, hi);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            e34[8 * w + i] = h2_as_u32(lo[i]);
+            e34[8 * w + 4 + i] = h2_as_u32(hi[i]);
+          }
+        }
+        store_v_rows(e12, e34);
+      }
     } else {
       const W4Group g12 = w4_group2(cur.vs[0], cur.vz[0], cur.vs[1], cur.vz[1]);
       const W4Group g34 = w4_group2(cur.vs[2], cur.vz[2], cur.vs[3], cur.vz[3]);
 #pragma unroll
       for (int w = 0; w < EV / 8; ++w) {
-        // codes 0..3 of both rows in one word, codes 4..7 in another: the word decoder then
-        // returns (row A code n, row B code n) pairs
         __half2 lo[4], hi[4];
-        dq_w4_word(__byte_perm(cur.v[0][w], cur.v[1][w], 0x5410), g12, kc, lo);  // codes 0,1,2,3 (order 0,1,2,3)
+        dq_w4_word(__byte_perm(cur.v[0][w], cur.v[1][w], 0x5410), g12, kc, lo);
         dq_w4_word(__byte_perm(cur.v[0][w], cur.v[1][w], 0x7632), g12, kc, hi);
-        // dq_w4_word's out[i] pairs code i of the low half with code i of the high half:
-        // out[0] = code 0, out[1] = code 1, out[2] = code 2, out[3] = code 3 of each row
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           v12[8 * w + i] = h2_as_u32(lo[i]);
@@ -526,27 +756,7 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
         }
       }
     }
-    if (HOOK && p.v_out && FMT != ATTN_FP16) {
-      // row 2c (+8): the low halves of v12 (v34); row 2c+1 (+9): the high halves
-#pragma unroll
-      for (int e0 = 0; e0 < EV; e0 += 8) {
-        uint4 a, b, cc, d;
-        a.x = __byte_perm(v12[e0], v12[e0 + 1], 0x5410), a.y = __byte_perm(v12[e0 + 2], v12[e0 + 3], 0x5410);
-        a.z = __byte_perm(v12[e0 + 4], v12[e0 + 5], 0x5410), a.w = __byte_perm(v12[e0 + 6], v12[e0 + 7], 0x5410);
-        b.x = __byte_perm(v12[e0], v12[e0 + 1], 0x7632), b.y = __byte_perm(v12[e0 + 2], v12[e0 + 3], 0x7632);
-        b.z = __byte_perm(v12[e0 + 4], v12[e0 + 5], 0x7632), b.w = __byte_perm(v12[e0 + 6], v12[e0 + 7], 0x7632);
-        cc.x = __byte_perm(v34[e0], v34[e0 + 1], 0x5410), cc.y = __byte_perm(v34[e0 + 2], v34[e0 + 3], 0x5410);
-        cc.z = __byte_perm(v34[e0 + 4], v34[e0 + 5], 0x5410), cc.w = __byte_perm(v34[e0 + 6], v34[e0 + 7], 0x5410);
-        d.x = __byte_perm(v34[e0], v34[e0 + 1], 0x7632), d.y = __byte_perm(v34[e0 + 2], v34[e0 + 3], 0x7632);
-        d.z = __byte_perm(v34[e0 + 4], v34[e0 + 5], 0x7632), d.w = __byte_perm(v34[e0 + 6], v34[e0 + 7], 0x7632);
-        const int d0 = EV * g + e0;
-        const size_t base = ((size_t)h * p.S + tb) * D + d0;
-        if (tb + 2 * c < t1) store8(p.v_out + base + (size_t)(2 * c) * D, a, p.wide);
-        if (tb + 2 * c + 1 < t1) store8(p.v_out + base + (size_t)(2 * c + 1) * D, b, p.wide);
-        if (tb + 2 * c + 8 < t1) store8(p.v_out + base + (size_t)(2 * c + 8) * D, cc, p.wide);
-        if (tb + 2 * c + 9 < t1) store8(p.v_out + base + (size_t)(2 * c + 9) * D, d, p.wide);
-      }
-    }
+    if (HOOK && p.v_out && FMT != ATTN_FP16 && !FOLD) store_v_rows(v12, v34);
     // out^T tile j: row g <-> d = EV*g + j, row g + 8 <-> d = EV*g + NT + j
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
@@ -558,7 +768,7 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   // Two buffers in turn: the next block's loads fly while this one is computed.
   const int step = MA_WARPS * MA_BLOCK;
   int tb = t0 + wid * MA_BLOCK;
-  BlockData<FMT, D> bufa, bufb;
+  Blk bufa, bufb;
   if constexpr (!MULTI) {
     if (tb < t1) fetch(bufa, tb, 0);
     while (tb < t1) {
@@ -622,7 +832,21 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       sm_ml[wid][0][0] = m[0];
       sm_ml[wid][0][1] = l[0];
     }
-    if (c == 0) {
+    if constexpr (FOLD) {
+      // rows g and g + 8 of every tile belong to group nv: their sums sit in column nv (lane nv / 2, element
+      // nv % 2); tiles with odd j were fed the nibbles that carry a factor 16
+      const int nv = (EV * g) >> p.gshift;
+      if (c == (nv >> 1)) {
+        const bool odd = (nv & 1) != 0;
+        const float zt = odd ? c1[1] : c1[0];
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          const float fj = (j & 1) ? 0.0625f : 1.0f;
+          sm_acc[wid][0][EV * g + j] = 16777216.0f * ((odd ? acc[j][1] : acc[j][0]) * fj - zt);
+          sm_acc[wid][0][EV * g + NT + j] = 16777216.0f * ((odd ? acc[j][3] : acc[j][2]) * fj - zt);
+        }
+      }
+    } else if (c == 0) {
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         sm_acc[wid][0][EV * g + j] = acc[j][0];
