@@ -263,9 +263,14 @@ def run_mine(args):
         if int(flag.item()) == 0:
             pg = None
     peer_mode = pg is not None
-    # The exchange as its own kernel after the GEMM (measured 15.0 us per step on two GPUs) or from the GEMM's
-    # epilogue (w4b_gemm_w4_push: one kernel per step, measured 16.9 us): the faster one is the default.
-    fused_exchange = os.environ.get("W4B_BENCH_EXCHANGE", "split") == "fused"
+    # The exchange as its own kernel after the GEMM ("split": 15.1 us per step on two GPUs), from the GEMM's
+    # epilogue ("fused", w4b_gemm_w4_push: one kernel per step, 16.7 us), or as its own kernel on a second stream
+    # beside the next step's GEMM ("overlap": 12.6 us): the fastest is the default.
+    exchange_mode = os.environ.get("W4B_BENCH_EXCHANGE", "overlap")
+    fused_exchange = exchange_mode == "fused"
+    # "overlap": the exchange kernel of step i runs on a second stream beside the GEMM of step i + 1 (a step's
+    # slice lives in one of three buffers, and the GEMM that reuses a buffer waits for the exchange that read it)
+    overlap_exchange = exchange_mode == "overlap"
     gathered = torch.empty(world, M, N, device=device, dtype=torch.float16) if (world > 1 and not peer_mode) else None
 
     def step(i, st=None):
@@ -352,8 +357,27 @@ def run_mine(args):
         with torch.cuda.stream(side):
             sstream = side.cuda_stream
             graph.capture_begin(capture_error_mode="thread_local")  # (NCCL's watchdog thread queries events meanwhile)
-            for i in range(args.steps):
-                step(i, sstream)
+            if peer_mode and overlap_exchange and not fused_exchange:
+                xstream = torch.cuda.Stream()
+                pushed = []  # the exchange kernels' completion events, by step
+                depth = w4.peer.NBUF  # the GEMM of step i rewrites the buffer that the exchange of step i - NBUF read
+                for i in range(args.steps):
+                    buf = i % w4.peer.NBUF
+                    if i >= depth:
+                        side.wait_event(pushed[i - depth])
+                    w4.gemm(packs[i % copies][3], x.data_ptr(), pg.slot(buf, rank), M, sstream)
+                    done = torch.cuda.Event()
+                    done.record(side)
+                    xstream.wait_event(done)
+                    pg.push(buf, xstream.cuda_stream)
+                    pushed.append(torch.cuda.Event())
+                    pushed[i].record(xstream)
+                join = torch.cuda.Event()
+                join.record(xstream)
+                side.wait_event(join)
+            else:
+                for i in range(args.steps):
+                    step(i, sstream)
             if peer_mode:
                 pg.wait(sstream)  # the graph ends when the last step's slices are here
             graph.capture_end()
@@ -450,7 +474,7 @@ def run_mine(args):
                                      "touched only after the previous kernel has completed)",
                    "timing": "one CUDA graph of K launches, CUDA events" if world == 1 else
                              "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks" if not peer_mode else
-                             ("one CUDA graph of K steps (one kernel per step: the GEMM, whose epilogue stores its output slice into every peer's arena over NVLink and posts the step; " if fused_exchange else "one CUDA graph of K steps (GEMM + peer all-gather kernel; ") + "a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
+                             ("one CUDA graph of K steps (one kernel per step: the GEMM, whose epilogue stores its output slice into every peer's arena over NVLink and posts the step; " if fused_exchange else ("one CUDA graph of K steps (GEMM + peer all-gather kernel; the exchange of step i runs on a second stream beside the GEMM of step i + 1; " if overlap_exchange else "one CUDA graph of K steps (GEMM + peer all-gather kernel; ")) + "a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
                    "parallelism": "single GPU" if world == 1 else
                                   f"column-parallel N x{world} + all-gather over NVLink peer stores" if peer_mode else
                                   f"column-parallel N x{world} + NCCL all-gather",
