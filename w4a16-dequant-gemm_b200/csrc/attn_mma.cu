@@ -162,6 +162,9 @@ struct BlockData<ATTN_F8, D> {
   }
 };
 
+template <int D, bool ASYM>
+struct W4Ring;
+
 template <int FMT, int D>
 struct BlockDataW4 {
   static constexpr int KW = D / 32, VW = D / 64;  // packed words per row
@@ -170,6 +173,17 @@ struct BlockDataW4 {
   uint32_t v[4][VW];
   __half ks[2], vs[4];
   uint32_t kz[2], vz[4];  // zero points
+  // from a stage of the lane-private ring
+  __device__ __forceinline__ void collect(uint32_t st, int lane, int g, int c, int gshift, int G) {
+    using R = W4Ring<D, FMT == ATTN_W4_ASYM>;
+    R::collect_codes(*this, st, lane);
+    const int gk = ((D / 4) * c) >> gshift, gv = ((D / 8) * g) >> gshift;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) ks[r] = R::k_scale(st, r, lane, gk), kz[r] = R::k_zero(st, r, lane, gk);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) vs[r] = R::v_scale(st, r, lane, gv), vz[r] = R::v_zero(st, r, lane, gv);
+    (void)G;
+  }
   __device__ __forceinline__ void load(const HeadBase& s, const int rk[2], const int rv[4], int g, int c,
                                        int gshift) {
 #pragma unroll
@@ -222,6 +236,21 @@ struct BlockDataW4Fold {
   uint32_t kz[2][2], vz[4];
   __half ks_own[HOOK ? 2 : 1], vs_own[HOOK ? 4 : 1];
   uint32_t kz_own[HOOK ? 2 : 1];
+  // from a stage of the lane-private ring (never with hooks)
+  __device__ __forceinline__ void collect(uint32_t st, int lane, int g, int c, int gshift, int G) {
+    using R = W4Ring<D, FMT == ATTN_W4_ASYM>;
+    R::collect_codes(*this, st, lane);
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        const int grp = (E * ((2 * c + x) & 3)) >> gshift;
+        ks[r][x] = R::k_scale(st, r, lane, grp), kz[r][x] = R::k_zero(st, r, lane, grp);
+      }
+    const int col = min(g, G - 1), gv = ((D / 8) * g) >> gshift;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) vs[r] = R::v_scale(st, r, lane, col), vz[r] = R::v_zero(st, r, lane, gv);
+  }
   __device__ __forceinline__ static uint32_t zero_of(const uint32_t* z, int row, int wG, int grp) {
     return FMT == ATTN_W4_ASYM ? ((__ldg(z + (size_t)(unsigned)(row * wG + (grp >> 3))) >> (4 * (grp & 7))) & 0xFu) : 8u;
   }
@@ -263,6 +292,86 @@ struct BlockDataW4Fold {
       vz[r] = zero_of(s.zv, rv[r], s.wG, grp);
       if (HOOK) vs_own[r % (HOOK ? 4 : 1)] = ldg_half(s.sv + (size_t)(unsigned)(rv[r] * s.G + grp));
     }
+  }
+};
+
+// ---------------------------------------------------------------------------
+// Lane-private shared-memory ring for the W4 forms (ASYNC): instead of holding the next block in registers, a
+// lane cp.async's exactly the pieces it will consume itself - its two K row quarters, its four V row eighths
+// and the scale (and zero-point) rows that belong to them - into its own slots of a stage, up to two blocks
+// ahead, and reads them back with shared-memory loads when the block's turn comes. No lane reads another
+// lane's slots, so cp.async.wait_group is the only synchronisation. Pieces are laid out [piece][lane] so that
+// a warp's load of one piece is conflict-free. Needs scale rows of at least four bytes (G >= 2).
+// ---------------------------------------------------------------------------
+template <int D, bool ASYM>
+struct W4Ring {
+  static constexpr int KB = D / 8, VB = D / 16;  // bytes per lane of a K row quarter / a V row eighth
+  static constexpr int OFF_V = 2 * 32 * KB;
+  static constexpr int OFF_SK = OFF_V + 4 * 32 * VB;
+  static constexpr int OFF_SV = OFF_SK + 2 * 32 * 8;
+  static constexpr int OFF_ZK = OFF_SV + 4 * 32 * 8;
+  static constexpr int OFF_ZV = OFF_ZK + 2 * 32 * 4;
+  static constexpr int STAGE = ASYM ? OFF_ZV + 4 * 32 * 4 : OFF_ZK;
+  static constexpr int DEPTH = 3;
+
+  __device__ __forceinline__ static void issue(uint32_t st, const HeadBase& s, const int rk[2], const int rv[4], int lane,
+                                               int g, int c) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      cp_async<KB>(st + r * 32 * KB + lane * KB, s.k + (size_t)(unsigned)rk[r] * (D / 2) + KB * c);
+      const __half* sp = s.sk + (size_t)(unsigned)(rk[r] * s.G);
+      if (s.G == 4)
+        cp_async<8>(st + OFF_SK + r * 256 + lane * 8, sp);
+      else
+        cp_async<4>(st + OFF_SK + r * 256 + lane * 8, sp);
+      if (ASYM) cp_async<4>(st + OFF_ZK + r * 128 + lane * 4, s.zk + (size_t)(unsigned)(rk[r] * s.wG));
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      cp_async<VB>(st + OFF_V + r * 32 * VB + lane * VB, s.v + (size_t)(unsigned)rv[r] * (D / 2) + VB * g);
+      const __half* sp = s.sv + (size_t)(unsigned)(rv[r] * s.G);
+      if (s.G == 4)
+        cp_async<8>(st + OFF_SV + r * 256 + lane * 8, sp);
+      else
+        cp_async<4>(st + OFF_SV + r * 256 + lane * 8, sp);
+      if (ASYM) cp_async<4>(st + OFF_ZV + r * 128 + lane * 4, s.zv + (size_t)(unsigned)(rv[r] * s.wG));
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  // the pieces every W4 block type shares
+  template <typename B>
+  __device__ __forceinline__ static void collect_codes(B& b, uint32_t st, int lane) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (KB == 16) {
+        const uint4 a = lds128(st + r * 32 * KB + lane * KB);
+        b.k[r][0] = a.x, b.k[r][1] = a.y, b.k[r][2 % B::KW] = a.z, b.k[r][3 % B::KW] = a.w;
+      } else {
+        const uint2 a = lds64(st + r * 32 * KB + lane * KB);
+        b.k[r][0] = a.x, b.k[r][1] = a.y;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      if (VB == 8) {
+        const uint2 a = lds64(st + OFF_V + r * 32 * VB + lane * VB);
+        b.v[r][0] = a.x, b.v[r][1 % B::VW] = a.y;
+      } else {
+        b.v[r][0] = lds32(st + OFF_V + r * 32 * VB + lane * VB);
+      }
+    }
+  }
+  __device__ __forceinline__ static __half k_scale(uint32_t st, int r, int lane, int grp) {
+    return __ushort_as_half(lds16(st + OFF_SK + r * 256 + lane * 8 + 2 * grp));
+  }
+  __device__ __forceinline__ static __half v_scale(uint32_t st, int r, int lane, int grp) {
+    return __ushort_as_half(lds16(st + OFF_SV + r * 256 + lane * 8 + 2 * grp));
+  }
+  __device__ __forceinline__ static uint32_t k_zero(uint32_t st, int r, int lane, int grp) {
+    return ASYM ? (lds32(st + OFF_ZK + r * 128 + lane * 4) >> (4 * grp)) & 0xFu : 8u;
+  }
+  __device__ __forceinline__ static uint32_t v_zero(uint32_t st, int r, int lane, int grp) {
+    return ASYM ? (lds32(st + OFF_ZV + r * 128 + lane * 4) >> (4 * grp)) & 0xFu : 8u;
   }
 };
 
@@ -309,7 +418,7 @@ __device__ __forceinline__ void store8(__half* dst, uint4 v, bool wide) {
   }
 }
 
-template <int FMT, int D, bool HOOK, bool MULTI>
+template <int FMT, int D, bool HOOK, bool MULTI, bool ASYNC>
 __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (FMT == ATTN_F8 ? 3 : 4)) attn_mma_kernel(const MmaParams p) {
   constexpr int E = D / 4;    // K elements per lane per row
   constexpr int EV = D / 8;   // V elements per lane per row
@@ -328,14 +437,19 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   using Blk = typename BlockSel<FMT, D, FOLD, HOOK>::type;
   constexpr int COLS = MULTI ? 8 : 1;  // sequences per CTA (columns of the products that carry distinct data)
   constexpr int NC = MULTI ? 2 : 1;    // columns whose softmax state a lane keeps (2c, 2c + 1)
+  using Ring = W4Ring<D, FMT == ATTN_W4_ASYM>;
+  extern __shared__ __align__(16) uint8_t sm_dyn[];  // ASYNC: the warps' rings; the merge reuses it afterwards
   __shared__ float sm_ml[MA_WARPS][COLS][2];
-  __shared__ float sm_acc[MA_WARPS][COLS][D];
+  __shared__ float sm_acc_static[ASYNC ? 1 : MA_WARPS][ASYNC ? 1 : COLS][ASYNC ? 1 : D];
+  float(*sm_acc)[COLS][D] = ASYNC ? reinterpret_cast<float(*)[COLS][D]>(sm_dyn)
+                                  : reinterpret_cast<float(*)[COLS][D]>(&sm_acc_static[0][0][0]);
   // MULTI: the last slices first - those past a shared prefix run once per sequence and take the longest
   const int sp = MULTI ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int g = lane >> 2, c = lane & 3;
   const AttnSource& s = p.src;
   const W4Consts kc = w4_consts();
+  const uint32_t ring = ASYNC ? smem_u32(sm_dyn) + (uint32_t)wid * (Ring::DEPTH * Ring::STAGE) : 0u;
   // MULTI: blockIdx.x = group * H + head, a group = eight consecutive sequences (fewer at the end). When their
   // lengths are equal they share one pass; otherwise each sequence gets a pass of its own with one live column.
   const int h = MULTI ? (int)(blockIdx.x % p.H) : (p.nseq ? (int)(blockIdx.x % p.H) : (int)blockIdx.x);
@@ -419,9 +533,9 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
-  auto fetch = [&](Blk& blk, int tb, int page_id) {
+  // rows of a block: K rows g, g + 8 and V rows 2c, 2c+1, 2c+8, 2c+9 of the 16 positions from tb
+  auto rows_of = [&](int tb, int page_id, int rk[2], int rv[4]) {
     const int last = t1 - 1;  // positions past the slice read a valid row and get weight 0
-    int rk[2], rv[4];
     if (MULTI || bt == nullptr || p.pshift >= 0) {
       // contiguous cache, or pages that are a power of two >= 16: the block's 16 positions (tb is a multiple of
       // 16) lie in one page, so one table entry serves the block (MULTI: the caller has looked it up)
@@ -445,10 +559,24 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       rv[2] = row(min(tb + 2 * c + 8, last));
       rv[3] = row(min(tb + 2 * c + 9, last));
     }
+  };
+  auto fetch = [&](Blk& blk, int tb, int page_id) {
+    int rk[2], rv[4];
+    rows_of(tb, page_id, rk, rv);
     blk.load(hb, rk, rv, g, c, p.gshift);
   };
+  // ASYNC: the same block into stage `slot` of this warp's ring (one cp.async group), and out of it
+  auto issue = [&](int slot, int tb, int page_id) {
+    int rk[2], rv[4];
+    rows_of(tb, page_id, rk, rv);
+    if constexpr (IS_W4) Ring::issue(ring + (uint32_t)slot * Ring::STAGE, hb, rk, rv, lane, g, c);
+  };
+  auto collect = [&](Blk& blk, int slot) {
+    if constexpr (ASYNC) blk.collect(ring + (uint32_t)slot * Ring::STAGE, lane, g, c, p.gshift, hb.G);
+  };
+  auto empty_group = [&]() { asm volatile("cp.async.commit_group;" ::: "memory"); };
+  auto wait_oldest = [&]() { asm volatile("cp.async.wait_group %0;" ::"n"(Ring::DEPTH - 1) : "memory"); };
 
-  // ucol: MULTI only - the one live column of this item, or -1 for every column of the pass
   // Hook stores of four V rows from (row 2c | row 2c+1) and (row 2c+8 | row 2c+9) pairs of halves
   auto store_v_rows_at = [&](const uint32_t* a12, const uint32_t* a34, int tb) {
 #pragma unroll
@@ -768,8 +896,35 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   // Two buffers in turn: the next block's loads fly while this one is computed.
   const int step = MA_WARPS * MA_BLOCK;
   int tb = t0 + wid * MA_BLOCK;
-  Blk bufa, bufb;
-  if constexpr (!MULTI) {
+  if constexpr (ASYNC && !MULTI) {
+    // blocks tb, tb + step, ... of this warp; DEPTH - 1 of them in flight ahead of the one being computed
+    Blk blk;
+    int ti = tb, slot = 0;
+#pragma unroll
+    for (int k = 0; k < Ring::DEPTH - 1; ++k) {
+      if (ti < t1) {
+        issue(k, ti, 0);
+        ti += step;
+      } else {
+        empty_group();
+      }
+    }
+    while (tb < t1) {
+      const int ahead = slot == 0 ? Ring::DEPTH - 1 : slot - 1;  // the stage freed by the previous block
+      if (ti < t1) {
+        issue(ahead, ti, 0);
+        ti += step;
+      } else {
+        empty_group();
+      }
+      wait_oldest();
+      collect(blk, slot);
+      compute(blk, tb, -1);
+      tb += step;
+      slot = slot == Ring::DEPTH - 1 ? 0 : slot + 1;
+    }
+  } else if constexpr (!MULTI) {
+    Blk bufa, bufb;
     if (tb < t1) fetch(bufa, tb, 0);
     while (tb < t1) {
       if (tb + step < t1) fetch(bufb, tb + step, 0);
@@ -805,6 +960,49 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       return true;
     };
     auto page_of = [&](int u) { return __shfl_sync(0xffffffffu, pages, u < 0 ? firstcol : u); };
+    if constexpr (ASYNC) {
+      // the item cursor (ti, ui) runs DEPTH - 1 items ahead of the item being computed
+      static_assert(Ring::DEPTH == 3, "two items in flight");
+      Blk blk;
+      int ti = tb, ui = 0, slot = 0;
+      bool more = tb < t1;
+      int t0q = 0, u0q = 0, t1q = 0, u1q = 0;  // the items in stages slot and slot + 1
+      bool have0 = false, have1 = false;
+      if (more) {
+        ui = classify(ti);
+        issue(0, ti, page_of(ui));
+        t0q = ti, u0q = ui, have0 = true;
+        more = advance(ti, ui);
+      } else {
+        empty_group();
+      }
+      if (more) {
+        issue(1, ti, page_of(ui));
+        t1q = ti, u1q = ui, have1 = true;
+        more = advance(ti, ui);
+      } else {
+        empty_group();
+      }
+      while (have0) {
+        const int ahead = slot == 0 ? 2 : slot - 1;
+        int t2q = 0, u2q = 0;
+        const bool have2 = more;
+        if (more) {
+          issue(ahead, ti, page_of(ui));
+          t2q = ti, u2q = ui;
+          more = advance(ti, ui);
+        } else {
+          empty_group();
+        }
+        wait_oldest();
+        collect(blk, slot);
+        compute(blk, t0q, u0q);
+        t0q = t1q, u0q = u1q, have0 = have1;
+        t1q = t2q, u1q = u2q, have1 = have2;
+        slot = slot == 2 ? 0 : slot + 1;
+      }
+    } else {
+    Blk bufa, bufb;
     int ucur = 0;
     bool have = tb < t1;
     if (have) {
@@ -823,6 +1021,11 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       compute(bufb, tb, ucur);
       tb = tn, ucur = un;
     }
+    }
+  }
+  if constexpr (ASYNC) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // every warp is done with its ring: the merge buffer lives there
   }
 
   // ---- warps of the CTA, merged in warp order (single form: every column of acc holds the same value) ----
@@ -894,23 +1097,51 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       part[2 + d] = a;
     }
   }
+  if (ASYNC && MULTI) __syncthreads();  // the next pass's ring reuses the merge buffer
   }  // pass
+}
+
+// The lane-private ring needs scale rows of at least four bytes at four-byte boundaries.
+static bool ring_ok(const MmaParams& p) {
+  const AttnSource& s = p.src;
+  if (s.G != 2 && s.G != 4) return false;
+  const uintptr_t need = s.G == 4 ? 7u : 3u;
+  return ((((uintptr_t)s.s_k | (uintptr_t)s.s_v) & need) == 0);
+}
+
+template <typename K>
+cudaError_t launch_ring(K kern, dim3 grid, size_t smem, const MmaParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, MA_THREADS, smem, stream>>>(p);
+  return cudaGetLastError();
 }
 
 template <int FMT, int D>
 cudaError_t launch_d(const MmaParams& p, cudaStream_t stream) {
   const dim3 grid((unsigned)(p.nseq ? p.nseq * p.H : p.H), (unsigned)p.splits);
   if constexpr (FMT == ATTN_W4_SYM || FMT == ATTN_W4_ASYM) {
+    using Ring = W4Ring<D, FMT == ATTN_W4_ASYM>;
+    const bool ring = ring_ok(p) && !(p.k_out || p.v_out);
+    const size_t ring_bytes = (size_t)MA_WARPS * Ring::DEPTH * Ring::STAGE;
     if (p.nseq > 1 && p.pshift >= 0) {  // sequences of one pool, eight to a CTA: shared pages are decoded once
       const dim3 ggrid((unsigned)(((p.nseq + 7) / 8) * p.H), (unsigned)p.splits);
-      attn_mma_kernel<FMT, D, false, true><<<ggrid, MA_THREADS, 0, stream>>>(p);
+      if (ring) {
+        const size_t merge_bytes = (size_t)MA_WARPS * 8 * D * sizeof(float);
+        return launch_ring(attn_mma_kernel<FMT, D, false, true, true>, ggrid, ring_bytes > merge_bytes ? ring_bytes : merge_bytes,
+                           p, stream);
+      }
+      attn_mma_kernel<FMT, D, false, true, false><<<ggrid, MA_THREADS, 0, stream>>>(p);
       return cudaGetLastError();
     }
+    // single sequence: measured faster with the ring only where zero-point rows add to the loads (asymmetric:
+    // 148 -> 135 us at B*H = 256, S = 8192); symmetric caches keep the register prefetch (100 vs 112 us)
+    if (ring && FMT == ATTN_W4_ASYM) return launch_ring(attn_mma_kernel<FMT, D, false, false, true>, grid, ring_bytes, p, stream);
   }
   if (p.k_out || p.v_out)
-    attn_mma_kernel<FMT, D, true, false><<<grid, MA_THREADS, 0, stream>>>(p);
+    attn_mma_kernel<FMT, D, true, false, false><<<grid, MA_THREADS, 0, stream>>>(p);
   else
-    attn_mma_kernel<FMT, D, false, false><<<grid, MA_THREADS, 0, stream>>>(p);
+    attn_mma_kernel<FMT, D, false, false, false><<<grid, MA_THREADS, 0, stream>>>(p);
   return cudaGetLastError();
 }
 

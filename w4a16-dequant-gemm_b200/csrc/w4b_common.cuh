@@ -346,6 +346,22 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 
 // 16-byte shared load executed only where `on` is set; elsewhere v keeps its value
 // and the lane generates no shared-memory traffic.
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ unsigned short lds16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+
 __device__ __forceinline__ void lds128_if(uint4& v, uint32_t addr, bool on) {
   asm volatile(
       "{\n"
