@@ -454,7 +454,10 @@ def run_mine(args):
         extra = sweep(torch, w4, device, packs, copies)
     if not args.no_sweep:
         del packs  # (room for the sharded problems)
-        extra["sharded"] = sharded_steps(torch, w4, device, world, rank, dist)
+        try:
+            extra["sharded"] = sharded_steps(torch, w4, device, world, rank, dist)
+        except Exception as e:  # noqa: BLE001  (secondary numbers must not take the headline line with them)
+            extra["sharded"] = {"error": f"{type(e).__name__}: {e}"}
 
     cpu = cpu_baseline(quick=True) if (rank == 0 and world == 1) else None
     if world > 1:
@@ -812,15 +815,52 @@ def sharded_steps(torch, w4, device, world, rank, dist):
     vnew = torch.randn(hl, D, device=device).to(torch.float16)
     last_row = int(bt[0, -1].item()) * page + page - 1  # the newest position of sequence 0
 
+    # N > 1: every sharded output is gathered on every rank by the peer-store exchange (one arena per output:
+    # the four linears' slices and the attention heads), each followed by the wait its consumer would need
+    gathers = None
+    if world > 1:
+        def exchange(handle):
+            res = [None] * world
+            dist.all_gather_object(res, handle)
+            return res
+        try:
+            sizes = [16 * max(w4.shard.row_range(Nf, world, rank)[1] - w4.shard.row_range(Nf, world, rank)[0], 64) * 2
+                     for Nf, _ in shapes]
+            gathers = [w4.peer.PeerGather(sz, rank, world, exchange) for sz in sizes]
+            gathers.append(w4.peer.PeerGather(nseq * hl * D * 2, rank, world, exchange))
+            ok = 1
+        except Exception as e:  # noqa: BLE001
+            print(f"bench: rank {rank}: no peer arenas for the decode step ({e})", file=sys.stderr)
+            gathers, ok = None, 0
+        flag = torch.tensor([ok], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            gathers = None
+
     def decode_step(i, s=None):
         lin_d, _, kvd = layers[i % nlayers]
-        w4.gemm(lin_d[0][2], x8.data_ptr(), lin_d[0][3].data_ptr(), 16, s)
+        buf = i % w4.peer.NBUF
+
+        def out_of(j):  # where linear j writes: its slot of the exchange arena, or a plain buffer
+            return gathers[j].slot(buf, rank) if gathers else lin_d[j][3].data_ptr()
+
+        def gather(j):
+            if gathers:
+                gathers[j].push(buf, s)
+                gathers[j].wait(s)
+
+        w4.gemm(lin_d[0][2], x8.data_ptr(), out_of(0), 16, s)
+        gather(0)
         w4.kv_append_w4(kvd, last_row, rows, knew.data_ptr(), vnew.data_ptr(), True, s)
         w4.attention_w4_flash_paged_batched(kvd, bt.data_ptr(), bt.shape[1], lens.data_ptr(), nseq, S, page, npages,
-                                            q.data_ptr(), o.data_ptr(), s)
-        w4.gemm(lin_d[1][2], x8.data_ptr(), lin_d[1][3].data_ptr(), 16, s)
-        w4.gemm(lin_d[2][2], x8.data_ptr(), lin_d[2][3].data_ptr(), 16, s)
-        w4.gemm(lin_d[3][2], x28.data_ptr(), lin_d[3][3].data_ptr(), 16, s)
+                                            q.data_ptr(), gathers[4].slot(buf, rank) if gathers else o.data_ptr(), s)
+        gather(4)
+        w4.gemm(lin_d[1][2], x8.data_ptr(), out_of(1), 16, s)
+        gather(1)
+        w4.gemm(lin_d[2][2], x8.data_ptr(), out_of(2), 16, s)
+        gather(2)
+        w4.gemm(lin_d[3][2], x28.data_ptr(), out_of(3), 16, s)
+        gather(3)
 
     for i in range(nlayers):
         decode_step(i)
@@ -831,7 +871,16 @@ def sharded_steps(torch, w4, device, world, rank, dist):
     out["C5_decode_step_graph"] = {"us_per_gpu_per_layer": round(us_step, 1), "kernel_launches_per_layer": int(per_step),
                                    "sum_of_separately_timed_parts_us": round(tot_us + us, 1), "layers_rotated": nlayers,
                                    "chain": "qkv linear, K/V append (device quantizer), batched paged attention, "
-                                            "o / gate-up / down linears; one CUDA graph, launch overlap on"}
+                                            "o / gate-up / down linears; one CUDA graph, launch overlap on",
+                                   "gathers": ("every sharded output all-gathered over NVLink peer stores inside the graph "
+                                               "(5 exchanges per layer)" if gathers else
+                                               ("none (one GPU)" if world == 1 else "not included: peer arenas unavailable"))}
+    if gathers:
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        for gth in gathers:
+            gth.close()
     assert w4.device_status() == 0
     return out
 
