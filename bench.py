@@ -266,8 +266,12 @@ def run_mine(args):
     # The exchange as its own kernel after the GEMM ("split": 15.1 us per step on two GPUs), from the GEMM's
     # epilogue ("fused", w4b_gemm_w4_push: one kernel per step, 16.7 us), or as its own kernel on a second stream
     # beside the next step's GEMM ("overlap": 12.6 us): the fastest is the default.
-    exchange_mode = os.environ.get("W4B_BENCH_EXCHANGE", "overlap")
+    exchange_mode = os.environ.get("W4B_BENCH_EXCHANGE", "carry")
     fused_exchange = exchange_mode == "fused"
+    # "carry": the GEMM of step i delivers the slice of step i - 1 to the peers while its weights stream
+    # (w4b_gemm_w4_carry: one kernel per step, no separate exchange launch); the last slice goes out with the
+    # exchange kernel
+    carry_exchange = exchange_mode == "carry"
     # "overlap": the exchange kernel of step i runs on a second stream beside the GEMM of step i + 1 (a step's
     # slice lives in one of three buffers, and the GEMM that reuses a buffer waits for the exchange that read it)
     overlap_exchange = exchange_mode == "overlap"
@@ -357,7 +361,12 @@ def run_mine(args):
         with torch.cuda.stream(side):
             sstream = side.cuda_stream
             graph.capture_begin(capture_error_mode="thread_local")  # (NCCL's watchdog thread queries events meanwhile)
-            if peer_mode and overlap_exchange and not fused_exchange:
+            if peer_mode and carry_exchange:
+                for i in range(args.steps):
+                    buf = i % w4.peer.NBUF
+                    pg.gemm_carry(packs[i % copies][3], x.data_ptr(), M, buf, (i - 1) % w4.peer.NBUF if i else None, sstream)
+                pg.push((args.steps - 1) % w4.peer.NBUF, sstream)
+            elif peer_mode and overlap_exchange and not fused_exchange:
                 xstream = torch.cuda.Stream()
                 pushed = []  # the exchange kernels' completion events, by step
                 depth = w4.peer.NBUF  # the GEMM of step i rewrites the buffer that the exchange of step i - NBUF read
@@ -477,7 +486,7 @@ def run_mine(args):
                                      "touched only after the previous kernel has completed)",
                    "timing": "one CUDA graph of K launches, CUDA events" if world == 1 else
                              "K eager steps (GEMM + NCCL all-gather), CUDA events, max over ranks" if not peer_mode else
-                             ("one CUDA graph of K steps (one kernel per step: the GEMM, whose epilogue stores its output slice into every peer's arena over NVLink and posts the step; " if fused_exchange else ("one CUDA graph of K steps (GEMM + peer all-gather kernel; the exchange of step i runs on a second stream beside the GEMM of step i + 1; " if overlap_exchange else "one CUDA graph of K steps (GEMM + peer all-gather kernel; ")) + "a step waits for the peers' previous slices, the graph for the last ones), CUDA events, max over ranks",
+                             ("one CUDA graph of K steps (one kernel per step: the GEMM of a step also delivers the previous step's slice to every peer's arena over NVLink peer stores while its weights stream, and posts it; the last slice goes out with the exchange kernel; " if carry_exchange else "one CUDA graph of K steps (one kernel per step: the GEMM, whose epilogue stores its output slice into every peer's arena over NVLink and posts the step; " if fused_exchange else ("one CUDA graph of K steps (GEMM + peer all-gather kernel; the exchange of step i runs on a second stream beside the GEMM of step i + 1; " if overlap_exchange else "one CUDA graph of K steps (GEMM + peer all-gather kernel; ")) + "a step waits for the peers' earlier slices, the graph for the last ones), CUDA events, max over ranks",
                    "parallelism": "single GPU" if world == 1 else
                                   f"column-parallel N x{world} + all-gather over NVLink peer stores" if peer_mode else
                                   f"column-parallel N x{world} + NCCL all-gather",

@@ -244,13 +244,13 @@ int w4b_attn_single_w4(const w4b_kv_w4* p, const void* q, void* out, void* strea
 
 /* ---- all-gather of the sharded GEMM's output over NVLink peer memory ----- */
 
-/* These seven entries have no counterpart in the reference (it is single-GPU). They
+/* These eight entries have no counterpart in the reference (it is single-GPU). They
  * are the exchange step of the column-parallel GEMM: one process per GPU, every
  * rank owns an arena that its peers map through CUDA IPC, and one launch per step
  * stores this rank's output slice into every peer's arena with plain peer stores
  * and posts a step flag. Before storing, a step waits (bounded, ~1 s, then the
- * device status word is set) for the peers' slices of the PREVIOUS step, so ranks
- * stay within one step of each other; with wait_now != 0 it also waits for the
+ * device status word is set) for the peers' slices of the step before the previous
+ * one, so ranks stay within two steps of each other; with wait_now != 0 it also waits for the
  * peers' slices of its own step (a complete all-gather in one launch).
  * w4b_allgather_wait does that wait on its own: after it, every slice of the last
  * pushed step is in this rank's arena. Graph-capturable: step numbers come from a
@@ -282,6 +282,17 @@ int w4b_allgather_wait(const void* flags_local, const void* counters, int rank, 
  * peers' slices of the previous step, so ranks stay within one step of each other; rotate over three slice
  * buffers. done: a zero-initialised 32-bit word in this rank's arena. c_peer, flag_dst are HOST arrays of
  * device pointers (entries [rank] ignored). */
+/* The sharded GEMM of step i with the exchange of step i - 1 inside it (no reference counterpart): w4b_gemm_w4
+ * through the stream kernel (M <= 16) into c, while one otherwise idle warp per CTA copies its share of
+ * `prev` - this rank's finished slice of the previous step, prev_bytes bytes in its own arena - to
+ * prev_peer[p], the same buffer in rank p's arena, and the last of them posts that step to flag_dst[p] (same
+ * flags and counters as w4b_allgather_push, with which it can be mixed; flow control as there). The
+ * transfer rides under the streaming of this step's weights: no separate launch, no end-of-kernel fence.
+ * prev_bytes == 0 carries nothing (the first step); the last step's slice is delivered by
+ * w4b_allgather_push, and w4b_allgather_wait completes a sequence. Rotate over three slice buffers. */
+int w4b_gemm_w4_carry(const w4b_packed_w4* p, const void* x, void* c, int M, const void* prev, size_t prev_bytes,
+                      void* const* prev_peer, void* const* flag_dst, const void* flags_local, void* counters,
+                      void* done, int rank, int world, void* stream);
 int w4b_gemm_w4_push(const w4b_packed_w4* p, const void* x, void* c, int M, void* const* c_peer,
                      void* const* flag_dst, const void* flags_local, void* counters, void* done, int rank,
                      int world, void* stream);

@@ -462,6 +462,78 @@ def test_gemm_push_loopback(oracle):
             flags = arenas[arena][lay["flags"]:lay["flags"] + 8 * world].view(torch.int64)
             assert int(flags[1 - arena]) == step
 
+def test_gemm_carry_loopback(oracle):
+    """The GEMM that carries the previous step's slice to the peers, on one GPU: two arenas stand for two ranks
+    that each own half of W's rows. A step launches rank 0's GEMM and then rank 1's on one stream; each delivers
+    its slice of the step before and waits only for flags that earlier launches have posted. The last slice goes
+    out with the exchange kernel. Afterwards every arena must hold both ranks' slices of every step, equal to
+    the plain GEMM's output bit for bit, over more steps than there are slice buffers."""
+    N, K, gs, M, world = 1024, 1024, 128, 4, 2
+    p = oracle.quantize_w4(oracle.normal_f64(N * K, 71) * 0.02, N, K, gs, False)
+    wts = W4Weights(p)
+    shards = [w4.shard.shard_w4(wts.desc, world, r) for r in range(world)]
+    nloc = shards[0].N
+    nbytes = M * nloc * 2
+    lay = w4.peer.arena_layout(nbytes, world)
+    arenas = [torch.zeros(lay["bytes"], dtype=torch.uint8, device="cuda") for _ in range(world)]
+    base = [a.data_ptr() for a in arenas]
+
+    def slot(arena, buf, owner):
+        return base[arena] + (buf * world + owner) * lay["slot"]
+
+    def args(r, buf):
+        o = 1 - r
+        dst, flag_dst = [0, 0], [0, 0]
+        dst[o] = slot(o, buf, r)
+        flag_dst[o] = base[o] + lay["flags"] + 8 * r
+        return dst, flag_dst
+
+    nsteps = 7
+    xs = [dev(oracle.normal_f16(M * K, 80 + i)) for i in range(nsteps)]
+    want = []
+    for i in range(nsteps):
+        per_rank = []
+        for r in range(world):
+            c = empty_f16(M * nloc)
+            w4.gemm(shards[r], ptr(xs[i]), ptr(c), M, path=w4.PATH_STREAM)
+            per_rank.append(bits(c).copy())
+        want.append(per_rank)
+    sync_ok()
+
+    def check(i):  # both slices of step i in both arenas
+        buf = i % w4.peer.NBUF
+        for r in range(world):
+            for owner in range(world):
+                off = (buf * world + owner) * lay["slot"]
+                got = arenas[r][off:off + nbytes].cpu().numpy().view(np.uint16)
+                assert np.array_equal(got, want[i][owner]), (i, r, owner)
+
+    for i in range(nsteps):
+        buf = i % w4.peer.NBUF
+        prev = (i - 1) % w4.peer.NBUF
+        for r in range(world):
+            dst, flag_dst = args(r, prev)
+            w4.capi.gemm_carry(shards[r], ptr(xs[i]), slot(r, buf, r), M, slot(r, prev, r) if i else None, nbytes if i else 0,
+                               dst if i else [0, 0], flag_dst, base[r] + lay["flags"], base[r] + lay["counters"],
+                               base[r] + lay["done"], r, world)
+        if i:
+            for r in range(world):  # step i - 1 is complete everywhere once both carries have run
+                w4.capi.allgather_wait(base[r] + lay["flags"], base[r] + lay["counters"], r, world)
+            sync_ok()
+            check(i - 1)
+    last = (nsteps - 1) % w4.peer.NBUF
+    for r in range(world):
+        dst, flag_dst = args(r, last)
+        w4.capi.allgather_push(slot(r, last, r), nbytes, dst, flag_dst, base[r] + lay["flags"], base[r] + lay["counters"],
+                               r, world, wait_now=False)
+    for r in range(world):
+        w4.capi.allgather_wait(base[r] + lay["flags"], base[r] + lay["counters"], r, world)
+    sync_ok()
+    check(nsteps - 1)
+    for r in range(world):
+        flags = arenas[r][lay["flags"]:lay["flags"] + 8 * world].view(torch.int64)
+        assert int(flags[1 - r]) == nsteps
+
 
 @pytest.mark.parametrize("world", [2, 3, 8])
 def test_sharded_descriptors_match_unsharded(oracle, world):

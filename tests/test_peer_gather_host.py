@@ -50,6 +50,24 @@ def test_push_contract():
         w4.peer.PeerGather(24, 0, 2, lambda h: [h, h])
 
 
+def test_gemm_carry_contract():
+    """The GEMM that carries the previous step's slice: rejected on the host before CUDA is touched."""
+    bad = w4.InvalidArgument
+    desc = w4.DevicePackedW(1024, 1024, 128, 8, 1, 4096, 8192, None)  # dummy addresses: never dereferenced
+    ok = dict(x=256, c=512, M=4, prev=1024, prev_bytes=8192, prev_peer=[0, 2048], flag_dst=[0, 4096], flags_local=8192,
+              counters=16384, done=32768, rank=0, world=2)
+
+    def call(**kw):
+        a = dict(ok, **kw)
+        w4.capi.gemm_carry(desc, a["x"], a["c"], a["M"], a["prev"], a["prev_bytes"], a["prev_peer"], a["flag_dst"],
+                           a["flags_local"], a["counters"], a["done"], a["rank"], a["world"])
+    for kw in (dict(M=0), dict(M=17), dict(world=1, prev_peer=[0], flag_dst=[0]), dict(rank=2), dict(prev=1028),
+               dict(prev_bytes=7), dict(prev_peer=[0, 0]), dict(flag_dst=[0, 4100]), dict(done=32770), dict(flags_local=8196),
+               dict(prev=None), dict(x=None)):
+        with pytest.raises(bad):
+            call(**kw)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -85,6 +85,8 @@ ABI = {
     "w4b_allgather_push": (_I, [_P, C.c_size_t, C.POINTER(_P), C.POINTER(_P), _P, _P, _I, _I, _I, _P]),
     "w4b_allgather_wait": (_I, [_P, _P, _I, _I, _P]),
     "w4b_gemm_w4_push": (_I, [C.POINTER(_PackedW4), _P, _P, _I, C.POINTER(_P), C.POINTER(_P), _P, _P, _P, _I, _I, _P]),
+    "w4b_gemm_w4_carry": (_I, [C.POINTER(_PackedW4), _P, _P, _I, _P, C.c_size_t, C.POINTER(_P), C.POINTER(_P), _P, _P, _P,
+                               _I, _I, _P]),
 }
 
 
@@ -351,6 +353,15 @@ def gemm_push(p: DevicePackedW, x, c, M, c_peer, flag_dst, flags_local, counters
     arr = _P * world
     _check(lib.w4b_gemm_w4_push(C.byref(p._c()), x, c, M, arr(*c_peer), arr(*flag_dst), flags_local, counters, done,
                                 rank, world, stream))
+
+
+def gemm_carry(p: DevicePackedW, x, c, M, prev, prev_bytes, prev_peer, flag_dst, flags_local, counters, done, rank, world,
+               stream=None):
+    """The sharded GEMM of a step with the exchange of the previous step inside it: `prev` (this rank's finished
+    slice of the previous step) goes to prev_peer[p] in every peer's arena while this step's weights stream."""
+    arr = _P * world
+    _check(lib.w4b_gemm_w4_carry(C.byref(p._c()), x, c, M, prev, prev_bytes, arr(*prev_peer), arr(*flag_dst), flags_local,
+                                 counters, done, rank, world, stream))
 
 
 def allgather_wait(flags_local, counters, rank, world, stream=None):

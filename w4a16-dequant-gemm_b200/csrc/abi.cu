@@ -733,6 +733,41 @@ int w4b_gemm_w4_push(const w4b_packed_w4* p, const void* x, void* c, int M, void
                   (cudaStream_t)stream, nullptr, "gemm push", &sp);
 }
 
+int w4b_gemm_w4_carry(const w4b_packed_w4* p, const void* x, void* c, int M, const void* prev, size_t prev_bytes,
+                      void* const* prev_peer, void* const* flag_dst, const void* flags_local, void* counters, void* done,
+                      int rank, int world, void* stream) {
+  if (int rc = check_w4(p, "gemm carry")) return rc;
+  if (!x || !c) INVALID("gemm carry: null pointer");
+  if (M < 1 || M > 16) INVALID("gemm carry: M must be 1..16 (the stream kernel's single pass)");
+  if (int rc = check_gemm_bounds(p->N, M, W4B_PATH_STREAM, "gemm carry")) return rc;
+  if (world < 2 || world > kMaxPeers) INVALID("gemm carry: world must be 2..%d", kMaxPeers);
+  if (rank < 0 || rank >= world) INVALID("gemm carry: rank out of range");
+  if (!flags_local || !counters || !done) INVALID("gemm carry: null pointer");
+  if ((((uintptr_t)flags_local | (uintptr_t)counters) & 7u) || ((uintptr_t)done & 3u))
+    INVALID("gemm carry: flags must be 8-byte aligned, the completion counter 4-byte aligned");
+  if (prev_bytes && (!prev || !prev_peer || !flag_dst)) INVALID("gemm carry: a slice to carry needs its source and destinations");
+  if (prev_bytes % 2 != 0 || ((uintptr_t)prev & 15u)) INVALID("gemm carry: the carried slice must be 16-byte aligned FP16 data");
+  StreamPeers sp;
+  memset(&sp, 0, sizeof(sp));
+  for (int r = 0; r < world && prev_bytes; ++r) {
+    if (r == rank) continue;
+    if (!prev_peer[r] || !flag_dst[r] || ((uintptr_t)prev_peer[r] & 15u) || ((uintptr_t)flag_dst[r] & 7u))
+      INVALID("gemm carry: bad destination for peer %d", r);
+    sp.c_peer[r] = (__half*)prev_peer[r];
+    sp.flag_dst[r] = (unsigned long long*)flag_dst[r];
+  }
+  sp.world = world;
+  sp.rank = rank;
+  sp.flags_local = flags_local;
+  sp.counters = (unsigned long long*)counters;
+  sp.done = (int*)done;
+  sp.carry = 1;
+  sp.prev_src = (const __half*)prev;
+  sp.prev_bytes = prev_bytes;
+  return run_gemm(p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, x, c, M, W4B_PATH_STREAM,
+                  (cudaStream_t)stream, nullptr, "gemm carry", &sp);
+}
+
 int w4b_allgather_wait(const void* flags_local, const void* counters, int rank, int world, void* stream) {
   if (world < 2 || world > kMaxPeers) INVALID("allgather wait: world must be 2..%d", kMaxPeers);
   if (rank < 0 || rank >= world) INVALID("allgather wait: rank out of range");

@@ -523,7 +523,65 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
     // adds their fragments in CTA order into shared memory and signals `collected`.
     const Handoff hand(walk, a.U, C, grid, (int)blockIdx.x);
     auto tile_live = [&](int panel, int t) { return panel * SK_ROWS + t * 16 < a.N; };
-    if (a.peers.world) {
+    if (a.peers.world && a.peers.carry) {
+      // Carry form: while the CTA's other warps stream this step's weights, this warp - which has nothing to do
+      // until the first fragments are parked, and whose hand-offs are only consumed at the other end of the
+      // grid's run - delivers its share of the PREVIOUS step's slice to every peer. Flow control as in the
+      // exchange kernel: rank p must have posted the step before the previous one (with three slice buffers
+      // nothing it may still read is then overwritten). Each warp makes its stores visible system-wide and
+      // counts itself; the warp that completes the count posts the step to every peer.
+      pdl_wait();  // the previous grid wrote the slice
+      if (a.peers.prev_bytes) {
+        if (lane < a.peers.world && lane != a.peers.rank) {
+          const volatile unsigned long long* flag = reinterpret_cast<const volatile unsigned long long*>(a.peers.flags_local) + lane;
+          const unsigned long long sent = *(reinterpret_cast<const volatile unsigned long long*>(a.peers.counters) + lane);
+          const long long t0 = clock64();
+          while (sent >= 2 && *flag + 1 < sent) {  // this delivery is step sent + 1: rank `lane` has posted sent - 1
+            __nanosleep(100);
+            if (clock64() - t0 > kWaitLimitCycles) {
+              atomicExch(a.status, ST_PEER_TIMEOUT);
+              break;
+            }
+          }
+        }
+        __syncwarp();
+        const size_t n16 = a.peers.prev_bytes >> 4;
+        const uint4* src = reinterpret_cast<const uint4*>(a.peers.prev_src);
+        const size_t nw = (size_t)gridDim.x * gridDim.y, me = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+        for (size_t i = me * 32 + lane; i < n16; i += nw * 32) {
+          const uint4 v = __ldcg(src + i);
+          for (int pr = 0; pr < a.peers.world; ++pr)
+            if (pr != a.peers.rank) reinterpret_cast<uint4*>(a.peers.c_peer[pr])[i] = v;
+        }
+        if (me == 0)  // a tail shorter than 16 bytes
+          for (size_t b = (n16 << 4) + 2 * lane; b < a.peers.prev_bytes; b += 64)
+            for (int pr = 0; pr < a.peers.world; ++pr)
+              if (pr != a.peers.rank)
+                *reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(a.peers.c_peer[pr]) + b) =
+                    *reinterpret_cast<const volatile __half*>(reinterpret_cast<const uint8_t*>(src) + b);
+        // Visibility, by the scoped memory model's causality order: this warp's copies precede its count at device
+        // scope (fence + atomic), the counting chain reaches the warp that completes it (atomic + fence), and that
+        // warp's system-scope releases of the flags carry everything that precedes them to the peers. The
+        // per-warp fences at device scope keep the 148 warps from each paying a system-scope fence (1.6 us on
+        // the kernel); the releases go out side by side, one lane per peer (one after the other they took
+        // 10 us for seven peers).
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = atomicAdd(a.peers.done, 1) == (int)nw - 1 ? 1 : 0;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          if (lane == 0) *a.peers.done = 0;  // ready for the next launch
+          if (lane < a.peers.world && lane != a.peers.rank) {
+            const unsigned long long step = a.peers.counters[lane] + 1ull;
+            asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peers.flag_dst[lane]), "l"(step) : "memory");
+            a.peers.counters[lane] = step;
+          }
+        }
+        __syncwarp();
+      }
+    } else if (a.peers.world) {
       // Exchange form: before this grid stores into the peers' arenas, every peer's slice of the previous step
       // must have arrived here - then no peer is more than one step behind and, with three slice buffers in
       // rotation, nothing a peer may still read is overwritten. In steady state the flags are long there.
@@ -917,7 +975,7 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
       }
     }
   }
-  if (a.peers.world) {
+  if (a.peers.world && !a.peers.carry) {
     // Exchange form: the CTA that finishes last sends the finished slice to every peer and posts the step. Every
     // consumer warp makes its part of c visible on this GPU; the CTA then counts itself at the grid's counter.
     // The CTA that completes the count sees the whole slice: its 256 consumer threads copy it into the peers'
@@ -965,14 +1023,11 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
       }
       __threadfence_system();
       named_barrier(BAR_DONE, 32 * SK_CONSUMERS);
-      if (tid == 0) {
-        *a.peers.done = 0;  // ready for the next launch
-        for (int pr = 0; pr < a.peers.world; ++pr) {
-          if (pr == a.peers.rank) continue;
-          const unsigned long long step = a.peers.counters[pr] + 1ull;
-          asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peers.flag_dst[pr]), "l"(step) : "memory");
-          a.peers.counters[pr] = step;
-        }
+      if (tid == 0) *a.peers.done = 0;  // ready for the next launch
+      if (tid < a.peers.world && tid != a.peers.rank) {  // one thread per peer: the releases' fences side by side
+        const unsigned long long step = a.peers.counters[tid] + 1ull;
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peers.flag_dst[tid]), "l"(step) : "memory");
+        a.peers.counters[tid] = step;
       }
     }
   }

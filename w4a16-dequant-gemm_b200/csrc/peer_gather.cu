@@ -2,12 +2,13 @@
 // step that follows the sharded GEMM (the reference is single-GPU and has no counterpart).
 //
 // Every rank owns an arena allocated with cudaMalloc and opened by its peers through CUDA IPC.
-// One launch per step: CTA p first waits (bounded) until rank p's slice of the PREVIOUS step has
-// landed here - in steady state it has, long ago - then stores this rank's slice into rank p's
-// arena with plain 16-byte peer stores, makes them visible system-wide and posts the step number
-// in p's flag array. Ranks therefore stay within one step of each other, a step never waits for
-// a round trip over NVLink, and with three slice buffers in rotation no slice is overwritten
-// while a peer may still read it. A second kernel waits for the slices of the current step (the
+// One launch per step: CTA p first waits (bounded) until rank p's slice of the step BEFORE THE
+// PREVIOUS one has landed here - in steady state it has, long ago - then stores this rank's slice
+// into rank p's arena with plain 16-byte peer stores, makes them visible system-wide and posts the
+// step number in p's flag array. Ranks therefore stay within two steps of each other and a step
+// never waits for a round trip over NVLink. Three slice buffers rotate: step i overwrites the slice
+// of step i - 3, and rank p posts step i - 2 only after everything it had queued on its stream for
+// the gathered data of step i - 3, so no slice is overwritten while a peer may still read it. A second kernel waits for the slices of the current step (the
 // end of a sequence, or whenever the gathered data is needed at once). Step numbers come from a
 // device-side counter, so the launches can be replayed from a CUDA graph. No TMA, no multicast,
 // no library kernel touches peer memory.
@@ -51,7 +52,7 @@ __global__ void __launch_bounds__(PP_THREADS) peer_push_kernel(const PeerPush a)
   uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0;
   if (i0 < a.n16) v0 = src[i0];
   if (i1 < a.n16) v1 = src[i1];
-  if (threadIdx.x == 0 && step > 1) await_flag(from_p, step - 1, a.status);  // rank p is at most a step behind
+  if (threadIdx.x == 0 && step > 2) await_flag(from_p, step - 2, a.status);  // rank p is at most two steps behind
   __syncthreads();
   if (i0 < a.n16) dst[i0] = v0;
   if (i1 < a.n16) dst[i1] = v1;

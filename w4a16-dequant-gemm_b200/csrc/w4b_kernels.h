@@ -57,6 +57,11 @@ struct StreamPeers {
   const void* flags_local;              // this rank's flag words, one uint64 per peer
   unsigned long long* counters;         // steps pushed to each peer so far, one uint64 per rank
   int* done;                            // grid completion counter in this rank's arena, zero between launches
+  // carry form: the grid delivers the PREVIOUS step's slice (prev_src, finished by the previous grid) into c_peer
+  // beside its own GEMM and posts that step; nothing is sent from the epilogue. prev_bytes == 0: nothing to carry.
+  int carry;
+  const __half* prev_src;
+  size_t prev_bytes;
 };
 struct StreamPlan {
   int streamed;       // 1: activations arranged by a pre-pass and streamed with the units; 0: resident in shared memory

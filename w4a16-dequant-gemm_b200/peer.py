@@ -4,8 +4,8 @@ One process per GPU. Every rank allocates an arena (three slice buffers of `worl
 64-bit flag and one 64-bit step counter per peer), exchanges its CUDA IPC handle through torch.distributed and
 maps the peers' arenas. A step is two launches on the caller's stream: the GEMM writes this rank's
 slice into its own slot, `push` stores it into every peer's slot and posts the step flag. A push
-first waits (bounded) for the peers' slices of the previous step, so ranks stay within one step of
-each other without any step waiting for a round trip over NVLink; `wait` (or `push(wait_now=True)`)
+first waits (bounded) for the peers' slices of the step before the previous one, so ranks stay within
+two steps of each other without any step waiting for a round trip over NVLink; `wait` (or `push(wait_now=True)`)
 waits for the slices of the current step. Steps rotate over three slice buffers, so a slice is never
 overwritten while a peer may still read it. No NCCL call is on the step, which makes a sequence of
 steps capturable in one CUDA graph.
@@ -68,6 +68,18 @@ class PeerGather:
         flag_dst = [0 if p == r else self.peers[p] + self.lay["flags"] + 8 * r for p in range(w)]
         capi.gemm_push(desc, x, self.slot(buf, r), M, dst, flag_dst, self.base + self.lay["flags"],
                        self.base + self.lay["counters"], self.base + self.lay["done"], r, w, stream)
+
+    def gemm_carry(self, desc, x, M, buf: int, prev_buf, stream=None):
+        """The sharded GEMM (stream kernel, M <= 16) writing this rank's slice of buffer `buf` into its own arena
+        while it delivers the slice of buffer `prev_buf` - finished by the previous step - to every peer and
+        posts that step (prev_buf None: nothing to deliver). The last step's slice goes out with push()."""
+        r, w = self.rank, self.world
+        have = prev_buf is not None
+        dst = [0 if (p == r or not have) else self.slot(prev_buf, r, self.peers[p]) for p in range(w)]
+        flag_dst = [0 if p == r else self.peers[p] + self.lay["flags"] + 8 * r for p in range(w)]
+        capi.gemm_carry(desc, x, self.slot(buf, r), M, self.slot(prev_buf, r) if have else None,
+                        self.slice_bytes if have else 0, dst, flag_dst, self.base + self.lay["flags"],
+                        self.base + self.lay["counters"], self.base + self.lay["done"], r, w, stream)
 
     def wait(self, stream=None):
         """Wait on the stream until every peer's slice of the last pushed step is here."""
