@@ -854,9 +854,8 @@ def sharded_steps(torch, w4, device, world, rank, dist):
             return gathers[j].slot(buf, rank) if gathers else lin_d[j][3].data_ptr()
 
         def gather(j):
-            if gathers:
-                gathers[j].push(buf, s)
-                gathers[j].wait(s)
+            if gathers:  # one kernel: deliver this rank's slice and wait for the peers' slices of the same step
+                gathers[j].push(buf, s, wait_now=True)
 
         w4.gemm(lin_d[0][2], x8.data_ptr(), out_of(0), 16, s)
         gather(0)
