@@ -1006,7 +1006,27 @@ def run_profile_case(args):
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     case = args.profile_case
-    if case.startswith("attn"):
+    if case == "attn_w4_batched":
+        # config 5's geometry on 16 heads: 64 sequences of 4608 positions = 256 shared prefix pages + 32 own pages of 16
+        H, D, g, page, nseq, SP, SU = 16, 128, 32, 16, 64, 4096, 512
+        G, S = D // g, SP + SU
+        npre, nown = SP // page, SU // page
+        npages = npre + nseq * nown
+        rows = npages * page
+        perm = torch.randperm(npages, device=device).to(torch.int32)
+        bt = torch.stack([torch.cat([perm[:npre], perm[npre + i * nown: npre + (i + 1) * nown]]) for i in range(nseq)]).contiguous()
+        lens = torch.full((nseq,), S, device=device, dtype=torch.int32)
+        qk = torch.randint(-2**31, 2**31 - 1, (H, rows, D // 8), device=device, dtype=torch.int32)
+        qv = torch.randint(-2**31, 2**31 - 1, (H, rows, D // 8), device=device, dtype=torch.int32)
+        sk = (torch.rand(H, rows, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        sv = (torch.rand(H, rows, G, device=device) * 0.1 + 0.05).to(torch.float16)
+        kv = w4.DeviceKVW4(H, S, D, g, G, 1, qk.data_ptr(), sk.data_ptr(), None, qv.data_ptr(), sv.data_ptr(), None)
+        q = torch.randn(nseq, H, D, device=device).to(torch.float16)
+        o = torch.empty(nseq, H, D, device=device, dtype=torch.float16)
+        call = lambda: w4.attention_w4_flash_paged_batched(kv, bt.data_ptr(), bt.shape[1], lens.data_ptr(), nseq, S, page,
+                                                           npages, q.data_ptr(), o.data_ptr())
+        workload = f"{case}: {nseq} sequences x {H} heads, S={S} ({SP} shared), D={D} gs={g} page={page}"
+    elif case.startswith("attn"):
         H, S, D, g = 128, 8192, 128, 32
         G = D // g
         q = torch.randn(H, D, device=device).to(torch.float16)
@@ -1053,7 +1073,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="run warmup + steps eager launches of the headline GEMM and exit (ncu target)")
-    ap.add_argument("--profile-case", default=None, choices=["attn_w4", "attn_f8", "attn_fp16", "gemm_tensor"],
+    ap.add_argument("--profile-case", default=None, choices=["attn_w4", "attn_w4_batched", "attn_f8", "attn_fp16", "gemm_tensor"],
                     help="run three eager launches of one secondary kernel on a small case and exit (ncu target)")
     args = ap.parse_args()
     if args.profile_case:

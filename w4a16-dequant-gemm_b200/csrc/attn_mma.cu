@@ -748,15 +748,19 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
       bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
       bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
       bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
-      if (bm > m[x]) {
-        const float corr = __expf(m[x] - bm);
+      // The reference point of a column's exponentials only moves when the block's maximum exceeds it by more
+      // than 8 (weights then stay below e^8, well inside FP16): with eight columns and slices of a few blocks a
+      // plain running maximum would rescale the accumulators on almost every item. A vote first, so that the
+      // rescale is a warp-uniform branch and not predicated multiplications on every item.
+      if (__any_sync(0xffffffffu, bm > m[x] + 8.0f)) {
+        const float corr = bm > m[x] + 8.0f ? __expf(m[x] - bm) : 1.0f;
         l[x] *= corr;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
           acc[j][x] *= corr;
           acc[j][2 + x] *= corr;
         }
-        m[x] = bm;
+        m[x] = bm > m[x] + 8.0f ? bm : m[x];
       }
       // a column that is not live gets weight 0 (its maximum may still be -inf)
       const __half2 pp = live ? __floats2half2_rn(__expf(s0 - m[x]), __expf(s1 - m[x])) : __floats2half2_rn(0.0f, 0.0f);
