@@ -93,6 +93,31 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t 
       : "memory");
 }
 
+// A operand in tensor memory (lane = row, 32-bit column = two consecutive k), B through a shared-memory descriptor
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(db), "r"(idesc), "r"((uint32_t)accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+
+// 32 columns of this thread's lane
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t v[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+      "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+      "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]),
+      "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]),
+      "r"(v[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -125,10 +150,9 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const int stages = a.stages;
   const uint32_t x_bytes = (uint32_t)a.mpad * 128u;
-  const uint32_t stage_bytes = TK_A_BYTES + x_bytes + TK_Q_BYTES;
+  const uint32_t stage_bytes = x_bytes + TK_Q_BYTES;
   const uint32_t sm_base = smem_u32(smem);
-  auto a_tile = [&](int s) { return sm_base + (uint32_t)s * stage_bytes; };
-  auto x_tile = [&](int s) { return a_tile(s) + TK_A_BYTES; };
+  auto x_tile = [&](int s) { return sm_base + (uint32_t)s * stage_bytes; };
   auto q_tile = [&](int s) { return x_tile(s) + x_bytes; };
   const uint32_t sm_bar = sm_base + (uint32_t)stages * stage_bytes;
   auto load_full = [&](int s) { return sm_bar + 8u * (uint32_t)s; };
@@ -156,9 +180,10 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_x);
   }
-  // TMEM: power-of-two column count >= 32 covering the Mpad accumulator columns
+  // TMEM: the Mpad accumulator columns, then one decoded operand tile (128 rows x 64 k = 32 columns) per stage;
+  // a power-of-two column count >= 32
   uint32_t ncols = 32;
-  while (ncols < (uint32_t)a.mpad) ncols <<= 1;
+  while (ncols < (uint32_t)a.mpad + 32u * (uint32_t)stages) ncols <<= 1;
   if (wid == TK_DECODERS + 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
                  "r"(ncols)
@@ -201,10 +226,11 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = make_smem_desc(a_tile(s)), db = make_smem_desc(x_tile(s));
+        const uint64_t db = make_smem_desc(x_tile(s));
+        const uint32_t ta = tmem_acc + (uint32_t)a.mpad + 32u * (uint32_t)s;
 #pragma unroll
-        for (int k = 0; k < TK_KC / 16; ++k)  // 32 bytes further along K inside the swizzle row
-          umma_f16(tmem_acc, da + 2u * k, db + 2u * k, idesc, kc > 0 || k > 0);
+        for (int k = 0; k < TK_KC / 16; ++k)  // 16 k = 8 columns of the operand tile, 32 bytes inside the swizzle row of x
+          umma_f16_ts(tmem_acc, ta + 8u * k, db + 2u * k, idesc, kc > 0 || k > 0);
         umma_commit(stage_free(s));  // arrives when the MMAs above have read the stage
         if (++s == stages) {
           s = 0;
@@ -258,7 +284,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
       }
       const uint4 c0 = lds128(q_tile(s) + (uint32_t)r * 32u), c1 = lds128(q_tile(s) + (uint32_t)r * 32u + 16u);
       const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-      const uint32_t arow = a_tile(s) + (uint32_t)r * 128u;
+      uint32_t arow[32];  // this row's 64 decoded halves
       const MxBlock mcur[2] = {mx_block(ecur[0]), mx_block(ecur[1])};
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
@@ -272,11 +298,13 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
           dq_w4_word(cw[w], fetch_w4(min(k0 / a.gs, a.G - 1)), kc4, o);
         }
         const uint4 v = unpair(o);
-        sts128(arow + (((uint32_t)w ^ ((uint32_t)r & 7u)) << 4), v);
+        arow[4 * w] = v.x, arow[4 * w + 1] = v.y, arow[4 * w + 2] = v.z, arow[4 * w + 3] = v.w;
         if (HOOK && blockIdx.y == 0 && n0 + r < a.N && k0 < a.K)  // K % 8 == 0: whole words are in range
           *reinterpret_cast<uint4*>(a.w_out + (size_t)(n0 + r) * a.K + k0) = v;
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor core reads
+      // the row goes to lane r of the stage's operand tile in tensor memory (the warp's lane quarter)
+      tmem_st32(tmem_acc + ((uint32_t)((wid & 3) * 32) << 16) + (uint32_t)a.mpad + 32u * (uint32_t)s, arow);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(a_ready(s));
       s += TK_GROUPS;
@@ -425,8 +453,9 @@ cudaError_t tensor_gemm_launch(int fmt, int gs, const uint32_t* q, const void* s
   tp.G = G;
   tp.mtile = M < 256 ? M : 256;
   tp.mpad = (tp.mtile + 15) / 16 * 16;
-  const size_t stage_bytes = TK_A_BYTES + (size_t)tp.mpad * 128 + TK_Q_BYTES;
+  const size_t stage_bytes = (size_t)tp.mpad * 128 + TK_Q_BYTES;  // (the decoded tile lives in tensor memory)
   int stages = (int)((232448 - 1024 - 8 * (3 * TK_MAX_STAGES + 2)) / stage_bytes);
+  if (tp.mpad + 32 * stages > 512) stages = (512 - tp.mpad) / 32;  // tensor memory: accumulator + one operand tile per stage
   // The ring depth is a multiple of the number of decode groups, so that a stage is always decoded by the
   // same group: a group then waits for fill n of a stage only after it has consumed fill n - 1 (an mbarrier
   // phase may be awaited at most one phase ahead - with more groups than stages a group would "pass" a wait
