@@ -82,14 +82,16 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
   return d;
 }
 
+// (The form without the disable-output-lane vector: with that operand an instruction occupied the issuing thread
+// for 185 cycles instead of 152, whatever the tile's width - measured in isolation.)
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, bool accumulate) {
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
       "}\n" ::"r"(tmem_d),
-      "l"(da), "l"(db), "r"(idesc), "r"((uint32_t)accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      "l"(da), "l"(db), "r"(idesc), "r"((uint32_t)accumulate)
       : "memory");
 }
 
@@ -99,9 +101,9 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
       "{\n"
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
       "}\n" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(db), "r"(idesc), "r"((uint32_t)accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      "r"(tmem_a), "l"(db), "r"(idesc), "r"((uint32_t)accumulate)
       : "memory");
 }
 
