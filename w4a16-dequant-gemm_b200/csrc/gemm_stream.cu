@@ -357,7 +357,7 @@ __device__ __forceinline__ uint4 x_arrange8(bool fold, uint4 v, float* sum8) {
 // activations of the pass's rows in the arrangement the consumers read (rows padded with zeros to 8 * MT) and,
 // for the folded formats, the FP32 sum of each row over each of the unit's four groups. The GEMM's loader then
 // brings a unit's block in with one bulk copy beside the unit's weights.
-constexpr int XA_THREADS = 64;
+constexpr int XA_THREADS = 512;  // one or two chunks per thread: with 64 threads a CTA walked 16 dependent loads, ~10 us per launch
 __global__ void __launch_bounds__(XA_THREADS)
     x_arrange_kernel(const __half* __restrict__ x, uint8_t* __restrict__ xa, int M, int K, int C, int xrows, int mt,
                      int fold) {
