@@ -15,7 +15,7 @@
 // scratch fits the array. With passes = ceil(M / 16) and mt = 2 when a pass holds
 // more than 8 rows, else 1:  passes * ceil(N / 64) * 4 counters <= 65,536;
 // passes * min(units, SMs) * mt * 4096 bytes of fragments <= 3 MiB; and, unless
-// M <= 8 rows of K <= ~8K activations stay resident in shared memory,
+// the activation rows stay resident in shared memory (one or two rows of a few thousand activations),
 // passes * (K / 512) * (8704 * mt + 256) bytes of arranged activations <= 1 MiB
 // (e.g. M <= 16, K <= 28,672, N <= 1,000,000 fits). Anything else is rejected
 // with W4B_INVALID and a message; nothing falls back to an allocating path.

@@ -1142,16 +1142,15 @@ void stream_gemm_plan(int N, int K, int M, int gs_or_0_for_mx, int sm_count, Str
   plan->grid_x = (int)(plan->U < sm_count ? plan->U : sm_count);
   plan->xpitch = xpitch;
   // Resident form: the activation rows stay in shared memory, re-arranged once per CTA. It is used while they
-  // are small (about 36 KB: one row of up to ~16K activations, four rows of 4K): staging them costs every CTA a
-  // pass over all of them, and they take room from the ring. One row that leaves a ring of kMinStagesHalf
-  // stages in half an SM's shared memory keeps to that half, so that the next launch's CTA sits beside this one.
-  if (M <= 8 && (size_t)M * xpitch <= 36 * 1024) {
+  // leave a ring of kMinStagesHalf stages in HALF an SM's shared memory (one or two rows of 4K activations), so
+  // that the next launch's CTA sits beside this one; beyond that the streamed form is faster (measured at
+  // N = 14336, K = 4096: M = 2 10.3 against 11.0 us, M = 3 11.7 against 10.9 us, M = 4 12.2 against 10.9 us).
+  if (M <= 8 && stages_for(M, K, stage, kSmemHalf) >= kMinStagesHalf) {
     plan->streamed = 0;
     plan->rows_per_pass = M;
     plan->mt = 1;
     plan->passes = 1;
-    int st = stages_for(M, K, stage, kSmemHalf);
-    if (st < kMinStagesHalf) st = stages_for(M, K, stage, kSmemOptIn);
+    const int st = stages_for(M, K, stage, kSmemHalf);
     plan->stages = st > SK_MAX_STAGES ? SK_MAX_STAGES : st;
     plan->smem = fixed_smem(M, K) + (size_t)plan->stages * stage;
     plan->xa_bytes = 0;
