@@ -355,12 +355,20 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
       __threadfence();
       const float* base = a.ws + (((size_t)blockIdx.y * gridDim.x + blockIdx.x) * a.splits) * (size_t)a.mpad * TK_ROWS;
       const int r = tid & (TK_ROWS - 1);
-      for (int col = tid >> 7; col < a.mtile; col += TK_DECODERS / 4) {
-        const int m = m0 + col;
-        if (m >= a.M) break;
-        float sum = 0.0f;
-        for (int sp = 0; sp < a.splits; ++sp) sum += __ldcg(base + ((size_t)sp * a.mpad + col) * TK_ROWS + r);
-        if (n0 + r < a.N) a.c[(size_t)m * a.N + n0 + r] = __float2half_rn(sum);
+      // eight columns at a time, their loads in flight together (one dependent load after the other, this loop
+      // cost more than the tile's MMAs); every column still adds its partials in split order
+      for (int col0 = 8 * (tid >> 7); col0 < a.mtile && m0 + col0 < a.M; col0 += 8 * (TK_DECODERS / 4)) {
+        float sum[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+        for (int sp = 0; sp < a.splits; ++sp)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum[i] += __ldcg(base + ((size_t)sp * a.mpad + col0 + i) * TK_ROWS + r);
+        if (n0 + r < a.N) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (col0 + i < a.mtile && m0 + col0 + i < a.M) a.c[(size_t)(m0 + col0 + i) * a.N + n0 + r] = __float2half_rn(sum[i]);
+        }
       }
     }
   }
