@@ -56,7 +56,15 @@ __global__ void __launch_bounds__(PP_THREADS) peer_push_kernel(const PeerPush a)
   __syncthreads();
   if (i0 < a.n16) dst[i0] = v0;
   if (i1 < a.n16) dst[i1] = v1;
-  for (size_t i = i1 + PP_THREADS; i < a.n16; i += PP_THREADS) dst[i] = src[i];
+  for (size_t i = i1 + PP_THREADS; i < a.n16; i += 8 * PP_THREADS) {  // the rest of a large slice, eight pieces in flight
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (i + (size_t)u * PP_THREADS < a.n16) v[u] = src[i + (size_t)u * PP_THREADS];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      if (i + (size_t)u * PP_THREADS < a.n16) dst[i + (size_t)u * PP_THREADS] = v[u];
+  }
   __syncthreads();
   if (threadIdx.x == 0) {
     // one system-scope release after the CTA barrier: the slice is visible to rank p before the flag is
