@@ -35,6 +35,8 @@
 // dequantisation hooks, paged or contiguous.
 #include <math_constants.h>
 
+#include <atomic>
+
 #include "w4b_common.cuh"
 #include "w4b_kernels.h"
 
@@ -1113,10 +1115,20 @@ static bool ring_ok(const MmaParams& p) {
   return ((((uintptr_t)s.s_k | (uintptr_t)s.s_v) & need) == 0);
 }
 
-template <typename K>
-cudaError_t launch_ring(K kern, dim3 grid, size_t smem, const MmaParams& p, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+// (one instantiation per kernel: the shared-memory opt-in is a per-device attribute of the function, set once)
+template <int FMT, int D, bool MULTI>
+cudaError_t launch_ring(dim3 grid, size_t smem, const MmaParams& p, cudaStream_t stream) {
+  auto kern = attn_mma_kernel<FMT, D, false, MULTI, true>;
+  static std::atomic<bool> configured[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    if (e != cudaSuccess) return e;
+    configured[dev].store(true, std::memory_order_release);
+  }
   kern<<<grid, MA_THREADS, smem, stream>>>(p);
   return cudaGetLastError();
 }
@@ -1132,15 +1144,14 @@ cudaError_t launch_d(const MmaParams& p, cudaStream_t stream) {
       const dim3 ggrid((unsigned)(((p.nseq + 7) / 8) * p.H), (unsigned)p.splits);
       if (ring) {
         const size_t merge_bytes = (size_t)MA_WARPS * 8 * D * sizeof(float);
-        return launch_ring(attn_mma_kernel<FMT, D, false, true, true>, ggrid, ring_bytes > merge_bytes ? ring_bytes : merge_bytes,
-                           p, stream);
+        return launch_ring<FMT, D, true>(ggrid, ring_bytes > merge_bytes ? ring_bytes : merge_bytes, p, stream);
       }
       attn_mma_kernel<FMT, D, false, true, false><<<ggrid, MA_THREADS, 0, stream>>>(p);
       return cudaGetLastError();
     }
     // single sequence: measured faster with the ring only where zero-point rows add to the loads (asymmetric:
     // 148 -> 135 us at B*H = 256, S = 8192); symmetric caches keep the register prefetch (100 vs 112 us)
-    if (ring && FMT == ATTN_W4_ASYM) return launch_ring(attn_mma_kernel<FMT, D, false, false, true>, grid, ring_bytes, p, stream);
+    if (ring && FMT == ATTN_W4_ASYM) return launch_ring<FMT, D, false>(grid, ring_bytes, p, stream);
   }
   if (p.k_out || p.v_out)
     attn_mma_kernel<FMT, D, true, false, false><<<grid, MA_THREADS, 0, stream>>>(p);

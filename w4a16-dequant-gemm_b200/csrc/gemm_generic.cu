@@ -15,6 +15,8 @@
 // whole words, so a half-used last word needs no special case), every lane keeps
 // four coalesced 4-byte loads in flight, words are decoded with the register
 // decoders (bit-identical to the scalar definitions) and accumulated in FP32.
+#include <atomic>
+
 #include "w4b_common.cuh"
 #include "w4b_kernels.h"
 
@@ -162,13 +164,19 @@ __global__ void __launch_bounds__(RG_THREADS, 2)
 }
 
 template <int FMT>
-cudaError_t row_gemm_launch(int mt, dim3 grid, size_t smem, const uint32_t* q, const void* scales, const uint32_t* zeros,
-                            int N, int K, int gshift, int G, const __half* x, __half* c, int M, cudaStream_t stream) {
+cudaError_t row_gemm_launch(int dev, int mt, dim3 grid, size_t smem, const uint32_t* q, const void* scales,
+                            const uint32_t* zeros, int N, int K, int gshift, int G, const __half* x, __half* c, int M,
+                            cudaStream_t stream) {
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
 #define W4B_ROW_CASE(MT)                                                                                          \
   case MT: {                                                                                                      \
-    cudaError_t e = cudaFuncSetAttribute(row_gemm_kernel<FMT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                         (int)RG_SMEM_MAX);                                                       \
-    if (e != cudaSuccess) return e;                                                                               \
+    static std::atomic<bool> configured[64]; /* the opt-in is a per-device attribute of the function */          \
+    if (!configured[dev].load(std::memory_order_acquire)) {                                                       \
+      const cudaError_t e = cudaFuncSetAttribute(row_gemm_kernel<FMT, MT>,                                        \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RG_SMEM_MAX);  \
+      if (e != cudaSuccess) return e;                                                                             \
+      configured[dev].store(true, std::memory_order_release);                                                     \
+    }                                                                                                             \
     row_gemm_kernel<FMT, MT><<<grid, RG_THREADS, smem, stream>>>(q, scales, zeros, N, K, gshift, G, x, c, M);     \
     return cudaGetLastError();                                                                                    \
   }
@@ -212,9 +220,9 @@ cudaError_t generic_gemm_launch(int fmt, int gs, const uint32_t* q, const void* 
     const size_t smem = (size_t)mt * 8 * (size_t)((K + 7) / 8) * sizeof(float);
     int gshift = 0;
     while (fmt != 2 && (1 << gshift) < gs) ++gshift;
-    if (fmt == 0) return row_gemm_launch<0>(mt, grid, smem, q, scales, zeros, N, K, gshift, G, x, c, M, stream);
-    if (fmt == 1) return row_gemm_launch<1>(mt, grid, smem, q, scales, zeros, N, K, gshift, G, x, c, M, stream);
-    return row_gemm_launch<2>(mt, grid, smem, q, scales, zeros, N, K, 5, G, x, c, M, stream);
+    if (fmt == 0) return row_gemm_launch<0>(dev, mt, grid, smem, q, scales, zeros, N, K, gshift, G, x, c, M, stream);
+    if (fmt == 1) return row_gemm_launch<1>(dev, mt, grid, smem, q, scales, zeros, N, K, gshift, G, x, c, M, stream);
+    return row_gemm_launch<2>(dev, mt, grid, smem, q, scales, zeros, N, K, 5, G, x, c, M, stream);
   }
   const unsigned gx = (unsigned)(((long long)N + GG_WARPS - 1) / GG_WARPS);
   long long gy = ((long long)M + GG_MTILE - 1) / GG_MTILE;
