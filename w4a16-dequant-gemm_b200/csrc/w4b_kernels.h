@@ -117,11 +117,16 @@ struct AttnSource {
   long long slab_rows;
 };
 // Slices per head of the split-S pass (the same on the host and, for the batched form, on the device).
-__host__ __device__ inline int attn_flash_splits(int H, int S, int sm_count) {
-  // About eight waves of CTAs at four resident CTAs per SM (a partial last wave then costs
-  // little), but slices as long as possible - 256 positions (four steps per warp), else 128, else
-  // 64 - as long as that still gives every SM two CTAs.
-  long long want = (32LL * sm_count + H - 1) / H;
+__host__ __device__ inline int attn_flash_splits(int H, int S, int sm_count, int per_sm = 14) {
+  // About per_sm CTAs per SM over the whole grid (3.5 waves at four resident CTAs per SM: a CTA pays its query
+  // loads, its first block's latency and its merge once, and with eight waves of short slices that was a
+  // quarter of its time - B*H = 256, S = 8192: 19 slices 97.7 us, 8 slices 90.8 us), but slices as long as
+  // possible - 256 positions (four steps per warp), else 128, else 64 - as long as that still gives every SM two
+  // CTAs.
+  long long want = ((long long)per_sm * sm_count + H - 1) / H;
+  // (no slice longer than 4096 positions: with few, long CTAs the last partial wave costs more than the merges
+  // saved - B*H = 512, S = 32768: 5 slices 620 us, 8 slices 596 us)
+  if (want < (S + 4095) / 4096) want = (S + 4095) / 4096;
   long long cap = 1;
   for (int slice = 256; slice >= 64; slice >>= 1) {
     cap = (S + slice - 1) / slice;
@@ -135,6 +140,9 @@ __host__ __device__ inline int attn_flash_splits(int H, int S, int sm_count) {
 // The batched paged form serves eight sequences of a head per CTA, so it cuts every sequence's slices for
 // ceil(nseq / 8) * H independent rows (a single sequence: H, the geometry of the single-sequence entry).
 __host__ __device__ inline int attn_batched_rows(int nseq, int H) { return ((nseq + 7) / 8) * H; }
+// ... at eight waves (the unshared tails of a group cost up to eight times a shared block, and shorter slices keep
+// them from running long after the rest); a single sequence keeps the single-sequence entry's geometry.
+__host__ __device__ inline int attn_batched_per_sm(int nseq) { return nseq > 1 ? 32 : 14; }
 size_t attn_flash_ws_bytes(int H, int D, int splits);
 cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
                               float* ws, __half* k_out, __half* v_out, cudaStream_t stream, int* launches);
