@@ -618,7 +618,7 @@ int w4b_attn_flash_w4_paged_batched(const w4b_kv_w4* p, const int* bt, int bt_st
             "call w4b_attn_flash_w4_paged per sequence otherwise");
   DeviceCtx* ctx = nullptr;
   if (int rc = get_ctx(&ctx)) return rc;
-  const int max_splits = attn_flash_splits(attn_batched_rows(nseq, p->H), max_seq_len, ctx->sm_count, attn_batched_per_sm(nseq));
+  const int max_splits = attn_flash_splits(attn_batched_rows(nseq, p->H), max_seq_len, ctx->sm_count);
   CUDA_TRY(ctx->attn_ws.reserve(attn_flash_ws_bytes(nseq * p->H, p->D, max_splits), false), "attention workspace");
   int launches = 0;
   CUDA_TRY(attn_flash_batched_launch(s, (const __half*)q, (__half*)out, p->H, p->D, nseq, seq_lens, bt_stride, max_splits,

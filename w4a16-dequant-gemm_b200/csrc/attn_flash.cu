@@ -254,8 +254,7 @@ __global__ void flash_combine_kernel(const float* __restrict__ ws, __half* __res
   __shared__ float sm_max[4];
   const int h = blockIdx.x;
   const float* hb = ws + (size_t)h * splits * (size_t)(D + 2);
-  if (seq_lens) splits = attn_flash_splits(attn_batched_rows((int)gridDim.x / H, H), __ldg(seq_lens + h / H), sm_count,
-                                             attn_batched_per_sm((int)gridDim.x / H));
+  if (seq_lens) splits = attn_flash_splits(attn_batched_rows((int)gridDim.x / H, H), __ldg(seq_lens + h / H), sm_count);
   if (splits == 1 && seq_lens) return;  // the slice pass wrote the output itself
   const size_t pitch = (size_t)(D + 2);
   float mx = -CUDART_INF_F, den = 0.0f;

@@ -484,7 +484,7 @@ __global__ void __launch_bounds__(MA_THREADS, (HOOK || FMT == ATTN_FP16) ? 2 : (
   const int firstcol = MULTI ? (npass == 1 ? 0 : pass) : 0;
   const int hx = MULTI ? (seq0 * p.H + h) : (int)blockIdx.x;  // hx: row of q / out (sequence-major in the batched form)
   const int S = MULTI ? __shfl_sync(0xffffffffu, my_len, firstcol) : (p.nseq ? __ldg(p.seq_lens + hx / p.H) : p.S);
-  const int splits = p.nseq ? attn_flash_splits(attn_batched_rows(p.nseq, p.H), S, p.sm_count, attn_batched_per_sm(p.nseq)) : p.splits;
+  const int splits = p.nseq ? attn_flash_splits(attn_batched_rows(p.nseq, p.H), S, p.sm_count) : p.splits;
   if (sp >= splits) continue;  // (batched: the grid is sized for the longest sequence)
   const int* bt = p.src.bt ? p.src.bt + (p.nseq ? (size_t)(MULTI ? seq0 : hx / p.H) * p.bt_stride : 0) : nullptr;
   // slices are cut at multiples of 64 positions: the four warps of a CTA get the same number of blocks

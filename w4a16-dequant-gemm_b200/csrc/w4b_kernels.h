@@ -140,9 +140,6 @@ __host__ __device__ inline int attn_flash_splits(int H, int S, int sm_count, int
 // The batched paged form serves eight sequences of a head per CTA, so it cuts every sequence's slices for
 // ceil(nseq / 8) * H independent rows (a single sequence: H, the geometry of the single-sequence entry).
 __host__ __device__ inline int attn_batched_rows(int nseq, int H) { return ((nseq + 7) / 8) * H; }
-// ... at eight waves (the unshared tails of a group cost up to eight times a shared block, and shorter slices keep
-// them from running long after the rest); a single sequence keeps the single-sequence entry's geometry.
-__host__ __device__ inline int attn_batched_per_sm(int nseq) { return nseq > 1 ? 32 : 14; }
 size_t attn_flash_ws_bytes(int H, int D, int splits);
 cudaError_t attn_flash_launch(const AttnSource& src, const __half* q, __half* out, int H, int S, int D, int splits,
                               float* ws, __half* k_out, __half* v_out, cudaStream_t stream, int* launches);
