@@ -195,6 +195,37 @@ int w4b_kv_append_w4(const w4b_kv_w4* p, long long row, long long slab_rows, con
 int w4b_kv_append_f8(const w4b_kv_f8* p, long long row, const void* k_new, const void* v_new,
                      int new_is_f16, void* stream);
 
+/* ---- offline re-layout of packed weights -------------------------------- */
+
+/* No counterpart in the reference (its kernels take any K with scalar loads;
+ * include/w4/fused.cuh:175-193 only asks for K >= 1). The fast kernels here are
+ * fed by TMA and need 16-byte row pitches and K % 512 == 0 (tensor kernel:
+ * K % 32 == 0); any other K runs the shape-agnostic kernels, far below the
+ * memory rate. These entries convert such a matrix once: the destination is the
+ * SAME matrix in the SAME packed format with K extended to dst->K by columns
+ * that dequantise to +0 exactly (the zero point, 8, or E2M1 +0 inside the
+ * source's partial last group; scale 0 / 2^0 with zero codes in new groups),
+ * so every entry of this library accepts it like any other descriptor.
+ *
+ * w4b_relayout_k: the K to convert to - the next multiple of 512 (-1: K < 1).
+ * w4b_relayout_w4 / _mx: src and dst are full descriptors; the caller owns the
+ *   destination buffers (q N*words(dst->K), scales N*dst->G, zeros N*words(dst->G);
+ *   MX: scales N*dst->B bytes) and fills N, gs, mode as in src, K = the extended
+ *   K, G / B consistent with it. Every destination word is written. dst->K may
+ *   be any value >= src->K. In place is rejected.
+ * w4b_gemm_w4_padded / _mx_padded: gemm / gemm_mx for activations of K_x <= p->K
+ *   columns (x: M rows of K_x FP16 values, the original K): a kernel copies them
+ *   into library scratch with zeros behind column K_x, then the GEMM of p runs.
+ *   The weight columns K_x.. meet zeros only, so the result is the product with
+ *   the original matrix. A caller that keeps its activations in rows of p->K
+ *   values, zeros behind K_x, calls w4b_gemm_w4 directly and saves that kernel.
+ *   No w_out hook here. */
+int w4b_relayout_k(int K);
+int w4b_relayout_w4(const w4b_packed_w4* src, const w4b_packed_w4* dst, void* stream);
+int w4b_relayout_mx(const w4b_packed_mx* src, const w4b_packed_mx* dst, void* stream);
+int w4b_gemm_w4_padded(const w4b_packed_w4* p, const void* x, int K_x, void* c, int M, int path, void* stream);
+int w4b_gemm_mx_padded(const w4b_packed_mx* p, const void* x, int K_x, void* c, int M, int path, void* stream);
+
 /* ---- decode attention, one query token per head ----------------------- */
 
 /* attention_fp16_flash (include/w4/kvflash.cuh:365-384): q H*D, k16/v16

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libw4b200.so")
-SOURCES = ["abi.cu", "dequant.cu", "gemm_generic.cu", "gemm_stream.cu", "gemm_noalloc.cu", "gemm_tensor.cu", "attn_flash.cu", "attn_mma.cu", "peer_gather.cu", "quantize.cu"]
+SOURCES = ["abi.cu", "dequant.cu", "gemm_generic.cu", "gemm_stream.cu", "gemm_noalloc.cu", "gemm_tensor.cu", "attn_flash.cu", "attn_mma.cu", "peer_gather.cu", "quantize.cu", "relayout.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared"]
 

@@ -71,6 +71,11 @@ ABI = {
     "w4b_quantize_f8": (_I, [_P, _I, _I, _I, _I, _P, _P, _P]),
     "w4b_kv_append_w4": (_I, [C.POINTER(_KvW4), C.c_longlong, C.c_longlong, _P, _P, _I, _P]),
     "w4b_kv_append_f8": (_I, [C.POINTER(_KvF8), C.c_longlong, _P, _P, _I, _P]),
+    "w4b_relayout_k": (_I, [_I]),
+    "w4b_relayout_w4": (_I, [C.POINTER(_PackedW4), C.POINTER(_PackedW4), _P]),
+    "w4b_relayout_mx": (_I, [C.POINTER(_PackedMx), C.POINTER(_PackedMx), _P]),
+    "w4b_gemm_w4_padded": (_I, [C.POINTER(_PackedW4), _P, _I, _P, _I, _I, _P]),
+    "w4b_gemm_mx_padded": (_I, [C.POINTER(_PackedMx), _P, _I, _P, _I, _I, _P]),
     "w4b_attn_flash_fp16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "w4b_attn_flash_w4": (_I, [C.POINTER(_KvW4), _P, _P, _P, _P, _P]),
     "w4b_attn_flash_f8": (_I, [C.POINTER(_KvF8), _P, _P, _P, _P, _P]),
@@ -293,6 +298,34 @@ def kv_append_w4(p: DeviceKVW4, row, slab_rows, k_new, v_new, f16=False, stream=
 
 def kv_append_f8(p: DeviceKVF8, row, k_new, v_new, f16=False, stream=None):
     _check(lib.w4b_kv_append_f8(C.byref(p._c()), row, k_new, v_new, int(f16), stream))
+
+
+# ---- offline re-layout: the same matrix zero-extended along K (no counterpart in the reference) ----
+
+def relayout_k(K: int) -> int:
+    """The K a matrix is extended to: the next multiple of 512."""
+    r = lib.w4b_relayout_k(K)
+    if r < 0:
+        raise InvalidArgument("relayout_k: bad K")
+    return r
+
+
+def relayout(src: DevicePackedW, dst: DevicePackedW, stream=None):
+    """Writes src, zero-extended along K to dst.K, into dst's buffers (same format, every word written)."""
+    _check(lib.w4b_relayout_w4(C.byref(src._c()), C.byref(dst._c()), stream))
+
+
+def relayout_mx(src: DevicePackedWm, dst: DevicePackedWm, stream=None):
+    _check(lib.w4b_relayout_mx(C.byref(src._c()), C.byref(dst._c()), stream))
+
+
+def gemm_padded(p: DevicePackedW, x, K_x, c, M, stream=None, path=PATH_AUTO):
+    """gemm for activations of K_x <= p.K columns: x is padded with zeros in library scratch first."""
+    _check(lib.w4b_gemm_w4_padded(C.byref(p._c()), x, K_x, c, M, path, stream))
+
+
+def gemm_mx_padded(p: DevicePackedWm, x, K_x, c, M, stream=None, path=PATH_AUTO):
+    _check(lib.w4b_gemm_mx_padded(C.byref(p._c()), x, K_x, c, M, path, stream))
 
 
 def device_status() -> int:

@@ -80,6 +80,7 @@ struct DeviceCtx {
   Scratch tensor_counters;  // per-tile arrival counters of the tensor GEMM's split-K form, zero between launches
   Scratch attn_ws;        // (m, l, acc[D]) partials of split sequences
   Scratch io_x, io_c;     // device staging of the host-buffer entry
+  Scratch gemm_xpad;      // zero-padded activation rows of the padded-K entries
 };
 
 constexpr int kMaxDevices = 64;
@@ -447,6 +448,88 @@ int w4b_kv_append_f8(const w4b_kv_f8* p, long long row, const void* k_new, const
            "kv f8 append kernel");
   g_launches += 2;
   return W4B_OK;
+}
+
+// ---- offline re-layout: the matrix zero-extended along K (no counterpart in the reference) ----
+
+int w4b_relayout_k(int K) {
+  if (K < 1 || K > INT_MAX - 511) return -1;
+  return (K + 511) / 512 * 512;
+}
+
+int w4b_relayout_w4(const w4b_packed_w4* src, const w4b_packed_w4* dst, void* stream) {
+  if (int rc = check_w4(src, "relayout source")) return rc;
+  if (int rc = check_w4(dst, "relayout destination")) return rc;
+  if (dst->N != src->N || dst->gs != src->gs || (dst->symmetric != 0) != (src->symmetric != 0))
+    INVALID("relayout: the destination must keep N, gs and the mode of the source");
+  if (dst->K < src->K) INVALID("relayout: destination K %d below the source's %d", dst->K, src->K);
+  if (dst->q == src->q || dst->scales == src->scales || (dst->zeros && dst->zeros == src->zeros))
+    INVALID("relayout: in place is not supported");
+  int launches = 0;
+  CUDA_TRY(relayout_launch(src->symmetric ? 0 : 1, src->gs, src->q, src->scales, src->zeros, src->N, src->K, src->G,
+                           (uint32_t*)dst->q, (void*)dst->scales, (uint32_t*)dst->zeros, dst->K, dst->G,
+                           (cudaStream_t)stream, &launches),
+           "relayout kernel");
+  g_launches += (unsigned long long)launches;
+  return W4B_OK;
+}
+
+int w4b_relayout_mx(const w4b_packed_mx* src, const w4b_packed_mx* dst, void* stream) {
+  if (int rc = check_mx(src, "relayout_mx source")) return rc;
+  if (int rc = check_mx(dst, "relayout_mx destination")) return rc;
+  if (dst->N != src->N) INVALID("relayout_mx: the destination must keep N");
+  if (dst->K < src->K) INVALID("relayout_mx: destination K %d below the source's %d", dst->K, src->K);
+  if (dst->q == src->q || dst->scales == src->scales) INVALID("relayout_mx: in place is not supported");
+  int launches = 0;
+  CUDA_TRY(relayout_launch(2, 32, src->q, src->scales, nullptr, src->N, src->K, src->B, (uint32_t*)dst->q,
+                           (void*)dst->scales, nullptr, dst->K, dst->B, (cudaStream_t)stream, &launches),
+           "relayout_mx kernel");
+  g_launches += (unsigned long long)launches;
+  return W4B_OK;
+}
+
+namespace {
+// Pads x (M rows of K_x halves) to the descriptor's K in library scratch; *xp is x itself when nothing is to pad.
+int pad_activations(const void* x, int K_x, int K, int M, cudaStream_t st, const void** xp, const char* who) {
+  if (K_x < 1 || K_x > K) INVALID("%s: K_x must be in 1..K of the descriptor", who);
+  if (K_x == K) {
+    *xp = x;
+    return W4B_OK;
+  }
+  DeviceCtx* ctx = nullptr;
+  if (int rc = get_ctx(&ctx)) return rc;
+  CUDA_TRY(ctx->gemm_xpad.reserve((size_t)M * K * sizeof(__half), false), "padded activations");
+  CUDA_TRY(pad_rows_launch((const __half*)x, (__half*)ctx->gemm_xpad.ptr, M, K_x, K, st), "pad kernel");
+  g_launches += 1;
+  *xp = ctx->gemm_xpad.ptr;
+  return W4B_OK;
+}
+}  // namespace
+
+int w4b_gemm_w4_padded(const w4b_packed_w4* p, const void* x, int K_x, void* c, int M, int path, void* stream) {
+  if (path < W4B_PATH_AUTO || path > W4B_PATH_GENERIC) INVALID("gemm padded: unknown path %d", path);
+  if (int rc = check_w4(p, "gemm padded")) return rc;
+  if (!x || !c) INVALID("gemm padded: null pointer");
+  if (M < 1) INVALID("gemm padded: bad M");
+  const int entry = resolve_path(path, M);
+  if (int rc = check_gemm_bounds(p->N, M, entry, "gemm padded")) return rc;
+  const void* xp = nullptr;
+  if (int rc = pad_activations(x, K_x, p->K, M, (cudaStream_t)stream, &xp, "gemm padded")) return rc;
+  return run_gemm(p->symmetric ? 0 : 1, p->gs, p->q, p->scales, p->zeros, p->N, p->K, p->G, xp, c, M, entry,
+                  (cudaStream_t)stream, nullptr, "gemm kernel");
+}
+
+int w4b_gemm_mx_padded(const w4b_packed_mx* p, const void* x, int K_x, void* c, int M, int path, void* stream) {
+  if (path < W4B_PATH_AUTO || path > W4B_PATH_GENERIC) INVALID("gemm_mx padded: unknown path %d", path);
+  if (int rc = check_mx(p, "gemm_mx padded")) return rc;
+  if (!x || !c) INVALID("gemm_mx padded: null pointer");
+  if (M < 1) INVALID("gemm_mx padded: bad M");
+  const int entry = resolve_path(path, M);
+  if (int rc = check_gemm_bounds(p->N, M, entry, "gemm_mx padded")) return rc;
+  const void* xp = nullptr;
+  if (int rc = pad_activations(x, K_x, p->K, M, (cudaStream_t)stream, &xp, "gemm_mx padded")) return rc;
+  return run_gemm(2, 32, p->q, p->scales, nullptr, p->N, p->K, p->B, xp, c, M, entry, (cudaStream_t)stream, nullptr,
+                  "gemm_mx kernel");
 }
 
 // ---- decode attention ------------------------------------------------------

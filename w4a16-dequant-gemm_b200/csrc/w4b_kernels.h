@@ -41,6 +41,15 @@ cudaError_t quantize_mx_launch(const void* w, int f16, int N, int K, uint32_t* q
 cudaError_t quantize_f8_launch(const void* x, int f16, int rows, int D, int gs, long long out_mul, long long out_add,
                                uint8_t* q, __half* scales, int* status, cudaStream_t stream);
 
+// ---- relayout.cu ---------------------------------------------------------------
+// The matrix zero-extended along K to Kp columns (Gp groups / blocks per row) in the same packed format.
+// fmt: 0 = W4 symmetric, 1 = W4 asymmetric, 2 = MXFP4 (gs ignored).
+cudaError_t relayout_launch(int fmt, int gs, const uint32_t* src_q, const void* src_scales, const uint32_t* src_zeros,
+                            int N, int K, int G, uint32_t* dst_q, void* dst_scales, uint32_t* dst_zeros, int Kp, int Gp,
+                            cudaStream_t stream, int* launches);
+// x (M rows of K halves) to xp (M rows of Kp halves), zeros behind column K.
+cudaError_t pad_rows_launch(const __half* x, __half* xp, int M, int K, int Kp, cudaStream_t stream);
+
 // ---- gemm_generic.cu --------------------------------------------------------
 // fmt: 0 = W4 symmetric, 1 = W4 asymmetric, 2 = MXFP4 (gs ignored, G = blocks per row).
 cudaError_t generic_gemm_launch(int fmt, int gs, const uint32_t* q, const void* scales, const uint32_t* zeros,
