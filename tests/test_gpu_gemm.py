@@ -203,6 +203,29 @@ def test_hostio_entry(oracle):
     ch = torch.empty(M * N, dtype=torch.int16).pin_memory()
     w4.gemm_hostio(wts.desc, xh.data_ptr(), ch.data_ptr(), M)  # page-locked: the kernel writes c_host itself
     assert np.array_equal(ch.numpy().view(np.uint16), c_dev)
+    # new values at the same page-locked address must be seen by the next call
+    x2 = oracle.normal_f16(M * K, 11)
+    c2_dev, _ = run_entry(w4.gemm, wts.desc, dev(x2), M, N, K, False)
+    xh.copy_(torch.from_numpy(x2.view(np.int16).copy()))
+    w4.gemm_hostio(wts.desc, xh.data_ptr(), ch.data_ptr(), M)
+    assert np.array_equal(ch.numpy().view(np.uint16), c2_dev)
+    # the same with launch overlap on: the GEMM may start early and waits for the copy before it reads x
+    prev = w4.set_launch_overlap(True)
+    try:
+        for xs, want in ((x, c_dev), (x2, c2_dev), (x, c_dev)):
+            xh.copy_(torch.from_numpy(xs.view(np.int16).copy()))
+            w4.gemm_hostio(wts.desc, xh.data_ptr(), ch.data_ptr(), M)
+            assert np.array_equal(ch.numpy().view(np.uint16), want)
+    finally:
+        w4.set_launch_overlap(prev)
+    # a larger M (tensor kernel)
+    Mb = 40
+    xb = oracle.normal_f16(Mb * K, 12)
+    cb_dev, _ = run_entry(w4.gemm, wts.desc, dev(xb), Mb, N, K, False)
+    xbh = torch.from_numpy(xb.view(np.int16).copy()).pin_memory()
+    cbh = torch.empty(Mb * N, dtype=torch.int16).pin_memory()
+    w4.gemm_hostio(wts.desc, xbh.data_ptr(), cbh.data_ptr(), Mb)
+    assert np.array_equal(cbh.numpy().view(np.uint16), cb_dev)
     xp, cp = x.copy(), np.zeros(M * N, np.uint16)  # pageable: staged through device memory
     w4.gemm_hostio(wts.desc, xp.ctypes.data, cp.ctypes.data, M)
     assert np.array_equal(cp, c_dev)
