@@ -195,3 +195,42 @@ def test_batched_paged_contract():
                dict(desc=w4.DeviceKVW4(2, 64, 128, 32, 4, 0, ONE * 16, ONE * 16, None, ONE * 16, ONE * 16, None))):  # asym, no zeros
         with pytest.raises(bad):
             call(**kw)
+
+
+def test_relayout_contract():
+    """The re-layout and the padded-K entries reject malformed calls on the host (dummy pointers)."""
+    assert w4.relayout_k(4100) == 4608 and w4.relayout_k(512) == 512 and w4.relayout_k(1) == 512
+    for k in (0, -5, INT32_MAX):
+        with pytest.raises(w4.InvalidArgument):
+            w4.relayout_k(k)
+    TWO = 2  # a second dummy address: the entries compare source and destination pointers
+    src = w4.DevicePackedW(2, 36, 8, 5, 0, ONE, ONE, ONE)
+
+    def dst(N=2, K=512, gs=8, G=64, sym=0, q=TWO, s=TWO, z=TWO):
+        return w4.DevicePackedW(N, K, gs, G, sym, q, s, z)
+
+    bad = w4.InvalidArgument
+    for d in (dst(N=3), dst(K=32, G=4), dst(gs=16, G=32), dst(sym=1, z=None), dst(G=63), dst(q=ONE), dst(s=ONE),
+              dst(z=ONE), dst(q=None)):
+        with pytest.raises(bad):
+            w4.relayout(src, d)
+    for name, p in variants()[1].items():          # a malformed source
+        with pytest.raises(bad):
+            w4.relayout(p, dst())
+    msrc = w4.DevicePackedWm(2, 40, 2, ONE, ONE)
+    for d in (w4.DevicePackedWm(3, 512, 16, TWO, TWO), w4.DevicePackedWm(2, 32, 1, TWO, TWO),
+              w4.DevicePackedWm(2, 512, 15, TWO, TWO), w4.DevicePackedWm(2, 512, 16, ONE, TWO),
+              w4.DevicePackedWm(2, 512, 16, TWO, None)):
+        with pytest.raises(bad):
+            w4.relayout_mx(msrc, d)
+    g = good()
+    for args in [(g, ONE, 0, ONE, 2), (g, ONE, 33, ONE, 2), (g, None, 32, ONE, 2), (g, ONE, 32, None, 2),
+                 (g, ONE, 32, ONE, 0)]:
+        with pytest.raises(bad):
+            w4.gemm_padded(*args)
+    with pytest.raises(bad):
+        w4.gemm_padded(g, ONE, 32, ONE, 2, path=9)
+    gm = w4.DevicePackedWm(2, 64, 2, ONE, ONE)
+    for args in [(gm, ONE, 0, ONE, 2), (gm, ONE, 65, ONE, 2), (gm, None, 64, ONE, 2), (gm, ONE, 64, ONE, 0)]:
+        with pytest.raises(bad):
+            w4.gemm_mx_padded(*args)
