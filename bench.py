@@ -1074,6 +1074,24 @@ def run_profile_case(args):
             v16 = torch.randn(H, S, D, device=device).to(torch.float16)
             call = lambda: w4.attention_fp16_flash(q.data_ptr(), k16.data_ptr(), v16.data_ptr(), o.data_ptr(), H, S, D)
         workload = f"{case}: H={H} S={S} D={D} gs={g}"
+    elif case == "gemm_stream_mx":  # config 3 at M = 1: the stream kernel's MXFP4 instantiation
+        N = K = 8192
+        M = 1
+        qp = torch.randint(-2**31, 2**31 - 1, (N, K // 8), device=device, dtype=torch.int32)
+        sc = torch.randint(118, 126, (N, K // 32), device=device, dtype=torch.uint8)
+        pk = w4.DevicePackedWm(N, K, K // 32, qp.data_ptr(), sc.data_ptr())
+        x = torch.randn(M, K, device=device).to(torch.float16)
+        c = torch.empty(M, N, device=device, dtype=torch.float16)
+        call = lambda: w4.gemm_mx(pk, x.data_ptr(), c.data_ptr(), M)
+        workload = f"gemm_stream_mx: MXFP4 N={N} K={K} M={M}"
+    elif case == "gemm_stream_m16":  # the headline weights at M = 16: streamed activations, two MMAs per step
+        N, K, gs, M = N_ROWS, K_COLS, GS, 16
+        qp, s, zp, _ = make_w4_asym(torch, N, K, gs, 1, device)
+        pk = w4.DevicePackedW(N, K, gs, K // gs, 0, qp.data_ptr(), s.data_ptr(), zp.data_ptr())
+        x = torch.randn(M, K, device=device).to(torch.float16)
+        c = torch.empty(M, N, device=device, dtype=torch.float16)
+        call = lambda: w4.gemm(pk, x.data_ptr(), c.data_ptr(), M)
+        workload = f"gemm_stream_m16: W4 asym gs={gs} N={N} K={K} M={M}"
     else:  # gemm_tensor: the headline weights at a prefill-sized M through the tensor kernel
         N, K, gs, M = N_ROWS, K_COLS, GS, 256
         qp, s, zp, _ = make_w4_asym(torch, N, K, gs, 1, device)
@@ -1099,7 +1117,8 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="run warmup + steps eager launches of the headline GEMM and exit (ncu target)")
-    ap.add_argument("--profile-case", default=None, choices=["attn_w4", "attn_w4_batched", "attn_f8", "attn_fp16", "gemm_tensor"],
+    ap.add_argument("--profile-case", default=None, choices=["attn_w4", "attn_w4_batched", "attn_f8", "attn_fp16", "gemm_tensor", "gemm_stream_mx",
+                                                                "gemm_stream_m16"],
                     help="run three eager launches of one secondary kernel on a small case and exit (ncu target)")
     args = ap.parse_args()
     if args.profile_case:
