@@ -58,6 +58,8 @@
 
 #include <atomic>
 
+#include <type_traits>
+
 #include "w4b_common.cuh"
 #include "w4b_kernels.h"
 
@@ -272,6 +274,10 @@ struct Groups<F_W4_SYM, GS> {
   __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts& k, __half2 out[4]) const {
     dq_w4_word(w, g[half], k, out);
   }
+  __device__ __forceinline__ bool all_fast() const { return false; }
+  __device__ __forceinline__ void decode_fast(uint32_t w, int half, const W4Consts& k, __half2 out[4]) const {
+    dq_w4_word(w, g[half], k, out);
+  }
 };
 
 template <int GS>
@@ -289,6 +295,10 @@ struct Groups<F_W4_ASYM, GS> {
   __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts& k, __half2 out[4]) const {
     dq_w4_word(w, g[half], k, out);
   }
+  __device__ __forceinline__ bool all_fast() const { return false; }
+  __device__ __forceinline__ void decode_fast(uint32_t w, int half, const W4Consts& k, __half2 out[4]) const {
+    dq_w4_word(w, g[half], k, out);
+  }
 };
 
 template <int GS>
@@ -300,6 +310,12 @@ struct Groups<F_MX, GS> {
   }
   __device__ __forceinline__ void decode(uint32_t w, int half, const W4Consts&, __half2 out[4]) const {
     dq_mx_word(w, b[half], out);
+  }
+  // Both blocks in the range of the bit-placement decode: a warp that finds this true for all its lanes decodes
+  // the chunk without the per-word choice of the form.
+  __device__ __forceinline__ bool all_fast() const { return b[0].fast && b[1].fast; }
+  __device__ __forceinline__ void decode_fast(uint32_t w, int half, const W4Consts&, __half2 out[4]) const {
+    dq_mx_word_fast(w, b[half], out);
   }
 };
 
@@ -863,11 +879,18 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
           Groups<FMT, GS> ga, gb;
           ga.load(meta + ra * SK_META_ROW, meta + SK_META_ZOFF + ra * 8, c, kh);
           gb.load(meta + (ra + 8) * SK_META_ROW, meta + SK_META_ZOFF + (ra + 8) * 8, c, kh);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          // MXFP4: one vote per chunk instead of a choice of the decode form per word
+          bool uniform_fast = false;
+          if constexpr (FMT == F_MX) uniform_fast = __all_sync(__activemask(), ga.all_fast() && gb.all_fast()) != 0;
+          auto step = [&](int i, auto fast_form) {
             __half2 pa[4], pb[4];
-            ga.decode(word_of(qa0, qa1, i), i >> 2, kc, pa);
-            gb.decode(word_of(qb0, qb1, i), i >> 2, kc, pb);
+            if constexpr (decltype(fast_form)::value) {
+              ga.decode_fast(word_of(qa0, qa1, i), i >> 2, kc, pa);
+              gb.decode_fast(word_of(qb0, qb1, i), i >> 2, kc, pb);
+            } else {
+              ga.decode(word_of(qa0, qa1, i), i >> 2, kc, pa);
+              gb.decode(word_of(qb0, qb1, i), i >> 2, kc, pb);
+            }
             if (HOOK && blockIdx.y == 0) {  // every pass decodes the same weights; one writes them
               const int k = ch * SK_KC + 64 * c + 8 * i;
               const int na = tile_row0 + rg, nb = na + 8;
@@ -891,6 +914,13 @@ __global__ void __launch_bounds__(SK_THREADS, 2)
               mma_16816(acc[mt][0], f0, xv.x, xv.y);
               mma_16816(acc[mt][1], f1, xv.z, xv.w);
             }
+          };
+          if (FMT == F_MX && uniform_fast) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) step(i, std::true_type{});
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) step(i, std::false_type{});
           }
         }
       }

@@ -182,17 +182,22 @@ __device__ __forceinline__ MxBlock mx_block(uint32_t se) {
   return b;
 }
 
+// The fast form alone, for callers that have established b.fast (for a whole warp, say).
+__device__ __forceinline__ void dq_mx_word_fast(uint32_t qw, const MxBlock& b, __half2 out[4]) {
+  const uint32_t kMag = 0x0E000E00u, kSign = 0x80008000u;
+  const uint32_t r0 = and_or(qw << 12, kSign, (qw << 9) & kMag);
+  const uint32_t r1 = and_or(qw << 8, kSign, (qw << 5) & kMag);
+  const uint32_t r2 = and_or(qw << 4, kSign, (qw << 1) & kMag);
+  const uint32_t r3 = and_or(qw, kSign, (qw >> 3) & kMag);
+  out[0] = __hmul2_rn(u32_as_h2(r0), b.h2);
+  out[1] = __hmul2_rn(u32_as_h2(r1), b.h2);
+  out[2] = __hmul2_rn(u32_as_h2(r2), b.h2);
+  out[3] = __hmul2_rn(u32_as_h2(r3), b.h2);
+}
+
 __device__ __forceinline__ void dq_mx_word(uint32_t qw, const MxBlock& b, __half2 out[4]) {
   if (b.fast) {
-    const uint32_t kMag = 0x0E000E00u, kSign = 0x80008000u;
-    const uint32_t r0 = and_or(qw << 12, kSign, (qw << 9) & kMag);
-    const uint32_t r1 = and_or(qw << 8, kSign, (qw << 5) & kMag);
-    const uint32_t r2 = and_or(qw << 4, kSign, (qw << 1) & kMag);
-    const uint32_t r3 = and_or(qw, kSign, (qw >> 3) & kMag);
-    out[0] = __hmul2_rn(u32_as_h2(r0), b.h2);
-    out[1] = __hmul2_rn(u32_as_h2(r1), b.h2);
-    out[2] = __hmul2_rn(u32_as_h2(r2), b.h2);
-    out[3] = __hmul2_rn(u32_as_h2(r3), b.h2);
+    dq_mx_word_fast(qw, b, out);
   } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
