@@ -71,6 +71,32 @@ def test_mx_reference_matrix(oracle, i):
     assert np.array_equal(outs["gemm_mx"], outs[winner])
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 33])
+def test_mx_block_exponents_outside_the_half_range(oracle, M):
+    """Blocks whose power of two is no FP16 value (tiny and huge rows beside ordinary ones): the kernels choose
+    between the bit-placement decode and the scalar definition - per word, or per chunk by a warp vote in the
+    stream kernel - and both must give dequant_one_mx's bits (mx.hpp:52-59) and the oracle's products."""
+    N, K = 192, 1024
+    w = (oracle.normal_f64(N * K, 0xE8 + M) * 0.02).reshape(N, K)
+    rows = np.arange(N)
+    w[rows % 5 == 1] *= 2.0 ** -45        # shared exponents far below the half range
+    w[rows % 5 == 3] *= 2.0 ** 9          # ... and above the range of the fast form
+    w[7, 512:544] *= 2.0 ** -60           # one odd block inside an ordinary row
+    p = oracle.quantize_mx(w.ravel(), N, K)
+    se = p["scales"]
+    assert (se < 89).any() and (se > 128).any() and ((se >= 89) & (se <= 128)).any()
+    wd = oracle.dequant_all_mx(p)
+    x = oracle.normal_f16(M * K, 0xE9 + M)
+    ref = oracle.gemm_oracle(x, M, K, wd, N)
+    wts, x_d = MxWeights(p), dev(x)
+    for name in ("gemm_fused_mx", "gemm_mma_mx"):
+        c, w_hook = run_entry(getattr(w4, name), wts.desc, x_d, M, N, K, True)
+        assert np.array_equal(w_hook, wd), name
+        assert cases.rel_l2(cases.f16(c), ref) <= TOL, name
+        c2, _ = run_entry(getattr(w4, name), wts.desc, x_d, M, N, K, False)
+        assert np.array_equal(c2, c), name
+
+
 # The stream kernel's family: K % 512 == 0, N >= 64 (ragged N tails, several panels, split panels),
 # every supported group size, M across the m-tile and multi-pass boundaries.
 STREAM_SHAPES = [(64, 512), (128, 512), (200, 512), (333, 1024), (1024, 2048), (2500, 512), (4096, 4096)]
